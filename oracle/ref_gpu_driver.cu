@@ -1,0 +1,115 @@
+// Launcher for the REFERENCE's own CUDA kernels (test infrastructure only).
+// The kernels are included from the reference checkout at build time
+// (-I<reference>/include -I<reference>/src); nothing of theirs is copied here.
+// It performs the launch sequence of reference src/main.cu:109-205 with the
+// feature flags chosen at run time instead of compile time, so that tests and
+// the benchmark can (a) read back the dropout mask the reference really applies
+// and (b) time the reference kernels, recompiled for sm_100a, on the same box.
+#include <cstdio>
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <curand_kernel.h>
+#include "utils.h"
+#include "init_curand_states.h"
+#include "flash_forward.h"
+#include "flash_forward_splitkv.h"
+
+typedef void (*ref_kernel_t)(mykernelParamType);
+
+template <int Bits>
+static ref_kernel_t pick_fwd() {
+    return forward_kernel<(Bits >> 5) & 1, (Bits >> 4) & 1, (Bits >> 3) & 1, (Bits >> 2) & 1, (Bits >> 1) & 1, Bits & 1>;
+}
+template <int Bits>
+static ref_kernel_t pick_split() {
+    return forward_kernel_splitkv<(Bits >> 5) & 1, (Bits >> 4) & 1, (Bits >> 3) & 1, (Bits >> 2) & 1, (Bits >> 1) & 1, Bits & 1>;
+}
+template <int... I>
+static ref_kernel_t table_fwd(int bits, std::integer_sequence<int, I...>) {
+    static const ref_kernel_t t[] = {pick_fwd<I>()...};
+    return t[bits];
+}
+template <int... I>
+static ref_kernel_t table_split(int bits, std::integer_sequence<int, I...>) {
+    static const ref_kernel_t t[] = {pick_split<I>()...};
+    return t[bits];
+}
+
+#define REF_CHECK(x) do { cudaError_t e_ = (x); if (e_ != cudaSuccess) { \
+    fprintf(stderr, "ref_gpu_driver: %s at line %d\n", cudaGetErrorString(e_), __LINE__); return -1; } } while (0)
+
+// split_num: the split count the caller chose (the reference's policy,
+// src/main.cu:391-422, is exported by libref.so); values < 1 mean 1.
+// Returns the split count used (>= 1) or a negative error.  time_us (optional)
+// receives the mean device time per launch over `iters` launches.
+extern "C" int ref_gpu_forward(const void* q, const void* k, const void* v, float* o,
+                               int B, int H, int N, int d, float scale, int causal,
+                               int window_left, int window_right, const float* slopes_dev,
+                               float p_dropout, unsigned long long seed, int split_num,
+                               int iters, float* time_us) {
+    mykernelParamType param = {};
+    param.Q = (half*)q; param.K = (half*)k; param.V = (half*)v; param.O = o;
+    param.N = N; param.d = d; param.Br = 128; param.Bc = 128;
+    param.Tc = (N + 127) / 128; param.Tr = (N + 127) / 128;
+    param.softmax_scale = scale;
+    param.window_size_left = window_left; param.window_size_right = window_right;
+    param.alibi_slopes_ptr = (float*)slopes_dev;
+    const bool local = window_left >= 0 || window_right >= 0;
+    const bool dropout = p_dropout > 0.0f;
+    if (split_num <= 0) split_num = 1;
+    curandStatePhilox4_32_10_t* states = nullptr;
+    float *O_tmp = nullptr, *L = nullptr, *M = nullptr;
+    if (dropout) {
+        int n_states = param.Tr * H * B * split_num;
+        REF_CHECK(cudaMalloc(&states, (size_t)n_states * sizeof(*states)));
+        init_curand_states<<<(n_states + 255) / 256, 256>>>(states, seed, n_states);
+        param.dropout_prob = p_dropout; param.states = states;
+    }
+    const int bits = (dropout << 5) | ((causal ? 1 : 0) << 4) | (local << 3) | ((slopes_dev ? 1 : 0) << 2) |
+                     ((N % 128 == 0) << 1) | (d % 32 == 0);
+    ref_kernel_t kern;
+    dim3 grid(param.Tr, H, B), block(256);
+    const int align_d = (d + 31) / 32 * 32;
+    const int smem = (128 + 256) * align_d * (int)sizeof(half) + 128 * align_d * (int)sizeof(float);
+    if (smem > 163840) return -2;
+    if (split_num == 1) {
+        kern = table_fwd(bits, std::make_integer_sequence<int, 64>{});
+    } else {
+        grid.x = param.Tr * split_num;
+        REF_CHECK(cudaMalloc(&O_tmp, (size_t)B * H * N * d * split_num * sizeof(float)));
+        REF_CHECK(cudaMalloc(&L, (size_t)B * H * N * split_num * sizeof(float)));
+        REF_CHECK(cudaMalloc(&M, (size_t)B * H * N * split_num * sizeof(float)));
+        param.O_tmp = O_tmp; param.L = L; param.M = M; param.split_num = split_num;
+        kern = table_split(bits, std::make_integer_sequence<int, 64>{});
+    }
+    REF_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dim3 cgrid(param.Tr, H, B);
+    cudaEvent_t e0, e1;
+    REF_CHECK(cudaEventCreate(&e0)); REF_CHECK(cudaEventCreate(&e1));
+    // first launch = the result that is read back; dropout streams advance afterwards
+    kern<<<grid, block, smem>>>(param);
+    if (split_num > 1) forward_kernel_splitkv_combine<<<cgrid, 128>>>(param);
+    REF_CHECK(cudaGetLastError());
+    REF_CHECK(cudaDeviceSynchronize());
+    if (iters > 0 && time_us) {
+        // timing runs write into a scratch O so the first-launch result stays intact
+        float* o_scratch = nullptr;
+        REF_CHECK(cudaMalloc(&o_scratch, (size_t)B * H * N * d * sizeof(float)));
+        param.O = o_scratch;
+        REF_CHECK(cudaEventRecord(e0));
+        for (int i = 0; i < iters; ++i) {
+            kern<<<grid, block, smem>>>(param);
+            if (split_num > 1) forward_kernel_splitkv_combine<<<cgrid, 128>>>(param);
+        }
+        REF_CHECK(cudaEventRecord(e1));
+        REF_CHECK(cudaEventSynchronize(e1));
+        float ms = 0.f;
+        REF_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+        *time_us = ms * 1000.0f / iters;
+        cudaFree(o_scratch);
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(states); cudaFree(O_tmp); cudaFree(L); cudaFree(M);
+    return split_num;
+}
