@@ -1,0 +1,95 @@
+"""ctypes binding of libfa_b200.so, the C-ABI declared in include/fa_b200.h.
+
+There is no fallback: if the library is missing or fails to load, importing the
+compute entry points raises."""
+import ctypes
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libfa_b200.so")
+
+FA_DTYPE_FP16, FA_DTYPE_BF16, FA_DTYPE_FP32 = 0, 1, 2
+FA_OK = 0
+
+#: every symbol include/fa_b200.h declares
+EXPORTS = ["fa_fwd", "fa_fwd_workspace_bytes", "fa_fwd_resolve_splits", "fa_num_splits_heuristic",
+           "fa_dropout_mask", "fa_merge_partial", "fa_cast_output", "fa_fwd_host", "fa_fwd_host_release",
+           "fa_strerror", "fa_version"]
+
+
+class FwdParams(ctypes.Structure):
+    """struct fa_fwd_params"""
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("o", ctypes.c_void_p),
+        ("lse", ctypes.c_void_p),
+        ("dtype", ctypes.c_int), ("o_dtype", ctypes.c_int),
+        ("batch", ctypes.c_int), ("heads", ctypes.c_int),
+        ("seqlen_q", ctypes.c_int), ("seqlen_k", ctypes.c_int),
+        ("head_dim", ctypes.c_int),
+        ("softmax_scale", ctypes.c_float),
+        ("is_causal", ctypes.c_int),
+        ("window_left", ctypes.c_int), ("window_right", ctypes.c_int),
+        ("alibi_slopes", ctypes.c_void_p),
+        ("p_dropout", ctypes.c_float),
+        ("seed", ctypes.c_uint64), ("offset", ctypes.c_uint64), ("unit0", ctypes.c_uint64),
+        ("num_splits", ctypes.c_int),
+        ("q_pos0", ctypes.c_int64), ("k_pos0", ctypes.c_int64),
+        ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
+        ("status", ctypes.c_void_p),
+        ("stream", ctypes.c_void_p),
+    ]
+
+
+class FaError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        super().__init__(f"{what} failed: {code} ({strerror(code)})")
+
+
+_lib = None
+
+
+def load():
+    """Loads the library (building nothing: run `python -m flash_attn_b200.build` first)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m flash_attn_b200.build`; "
+                          "there is no non-CUDA fallback")
+    L = ctypes.CDLL(LIB_PATH)
+    pp = ctypes.POINTER(FwdParams)
+    L.fa_fwd.argtypes = [pp]
+    L.fa_fwd.restype = ctypes.c_int
+    L.fa_fwd_host.argtypes = [pp]
+    L.fa_fwd_host.restype = ctypes.c_int
+    L.fa_fwd_host_release.argtypes = []
+    L.fa_fwd_host_release.restype = None
+    L.fa_fwd_workspace_bytes.argtypes = [pp]
+    L.fa_fwd_workspace_bytes.restype = ctypes.c_size_t
+    L.fa_fwd_resolve_splits.argtypes = [pp]
+    L.fa_fwd_resolve_splits.restype = ctypes.c_int
+    L.fa_num_splits_heuristic.argtypes = [ctypes.c_int] * 5
+    L.fa_num_splits_heuristic.restype = ctypes.c_int
+    L.fa_dropout_mask.argtypes = [pp, ctypes.c_void_p]
+    L.fa_dropout_mask.restype = ctypes.c_int
+    L.fa_merge_partial.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                   ctypes.c_int64, ctypes.c_int, ctypes.c_void_p]
+    L.fa_merge_partial.restype = ctypes.c_int
+    L.fa_cast_output.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p]
+    L.fa_cast_output.restype = ctypes.c_int
+    L.fa_strerror.argtypes = [ctypes.c_int]
+    L.fa_strerror.restype = ctypes.c_char_p
+    L.fa_version.argtypes = []
+    L.fa_version.restype = ctypes.c_int
+    _lib = L
+    return L
+
+
+def strerror(code):
+    return load().fa_strerror(int(code)).decode()
+
+
+def check(code, what):
+    if code != FA_OK:
+        raise FaError(code, what)

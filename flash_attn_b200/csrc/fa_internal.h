@@ -1,0 +1,49 @@
+// Internal declarations shared by the C-ABI translation unit and the kernels.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "philox.cuh"
+
+namespace fa {
+
+constexpr int kTile = 128;  // Br = Bc = 128, as the reference fixes them (src/main.cu:116-117)
+
+// Device-side argument block of the tiled forward kernel (the successor of
+// mykernelParamType, include/utils.h:21-44).  Q/K/V travel as TMA tensor maps.
+struct FwdArgs {
+    void* o;                // [units, Nq, d] in o dtype (non-split)
+    float* lse;             // [units, Nq] or null
+    float* o_partial;       // [units, splits, Nq, d] fp32 (split)
+    float* lse_partial;     // [units, splits, Nq]
+    const float* alibi_slopes;
+    int* status;
+    int heads;
+    int seqlen_q, seqlen_k, head_dim;
+    int tr, tc;             // query / key tiles
+    int num_splits, tiles_per_split;
+    float scale_log2;       // softmax_scale * log2(e)
+    int is_causal, window_left, window_right;
+    long long q_pos0, k_pos0;
+    int o_is_fp32;
+    DropoutParams drop;
+};
+
+// Launchers implemented in the .cu files; all return a cudaError_t.
+cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                             int units, bool bf16, bool dropout, cudaStream_t stream);
+
+struct CombineArgs {
+    const float* o_partial; const float* lse_partial;
+    void* o; float* lse;
+    long long rows_per_unit;   // Nq
+    int num_splits, head_dim;
+    int o_dtype;               // FA_DTYPE_*
+};
+cudaError_t launch_combine(const CombineArgs& a, long long units, cudaStream_t stream);
+cudaError_t launch_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int part_dtype,
+                         long long rows, int d, cudaStream_t stream);
+cudaError_t launch_cast(const float* src, void* dst, int o_dtype, long long n, cudaStream_t stream);
+cudaError_t launch_dropout_mask(const FwdArgs& a, uint8_t* keep, long long units, cudaStream_t stream);
+
+}  // namespace fa

@@ -1,0 +1,137 @@
+/*
+ * fa_b200 -- Blackwell (sm_100a) flash-attention forward behind a plain C ABI.
+ *
+ * This header is the drop-in boundary for the launcher surface of
+ * Yhorm26/flash_attn.  The reference has no library: its "API" is the kernel
+ * argument block mykernelParamType (include/utils.h:21-44) plus the launch code
+ * in main() (src/main.cu:109-205).  Each entry point below names the reference
+ * item it replaces.  All pointers are plain device (or, where stated, host)
+ * pointers; there are no C++ or framework types in any signature.
+ *
+ * Tensor layout (same as the reference, src/flash_forward.h:57-59):
+ *   Q, O : [batch, heads, seqlen_q, head_dim]  contiguous
+ *   K, V : [batch, heads, seqlen_k, head_dim]  contiguous
+ *   LSE  : [batch, heads, seqlen_q]            fp32
+ * Ownership: the caller owns every buffer including the workspace; the library
+ * allocates nothing in fa_fwd and keeps no state between calls (there is no RNG
+ * state array: dropout is a function of (seed, offset) only).
+ */
+#ifndef FA_B200_H
+#define FA_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_B200_VERSION 100
+
+/* element types */
+#define FA_DTYPE_FP16 0
+#define FA_DTYPE_BF16 1
+#define FA_DTYPE_FP32 2 /* output only: the reference writes O as fp32 (include/utils.h:26) */
+
+/* return codes: 0 on success, negative on failure; the library never exits or prints
+ * (the reference's CUDA_CHECK, src/main.cu:18-25, calls exit(1)). */
+#define FA_OK 0
+#define FA_ERR_INVALID_ARG (-1)    /* NULL pointer, non-positive size, bad enum, misaligned pointer */
+#define FA_ERR_UNSUPPORTED (-2)    /* head_dim > 128 or not a multiple of 8, dtype combination     */
+#define FA_ERR_WORKSPACE (-3)      /* workspace missing or smaller than fa_fwd_workspace_bytes()   */
+#define FA_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed                            */
+#define FA_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait gave up (read from *status)       */
+#define FA_ERR_NOT_SM100 (-6)      /* the current device is not compute capability 10.x            */
+#define FA_ERR_TOO_LARGE (-7)      /* size beyond a fixed limit of the entry point                 */
+
+/*
+ * Launch description.  Replaces mykernelParamType (include/utils.h:21-44) and the
+ * grid dimensions the reference passes beside it (batch = gridDim.z, heads =
+ * gridDim.y, src/main.cu:142).  Zero-initialise, then fill.
+ */
+typedef struct fa_fwd_params {
+    const void* q;            /* device, dtype                                   (param.Q) */
+    const void* k;            /* device, dtype                                   (param.K) */
+    const void* v;            /* device, dtype                                   (param.V) */
+    void* o;                  /* device, o_dtype                                 (param.O) */
+    float* lse;               /* device fp32 [B,H,Nq] or NULL; natural-log sum-exp of the
+                                 scaled, biased, masked scores; -inf for fully masked rows */
+    int dtype;                /* FA_DTYPE_FP16 | FA_DTYPE_BF16 */
+    int o_dtype;              /* same as dtype, or FA_DTYPE_FP32 */
+    int batch, heads;
+    int seqlen_q, seqlen_k;   /* the reference has one N for both (param.N) */
+    int head_dim;             /* multiple of 8, <= 128                              (param.d) */
+    float softmax_scale;      /* > 0                                    (param.softmax_scale) */
+    int is_causal;            /* masks k_pos > q_pos      (template flag Is_causal, main.cu:45) */
+    int window_left;          /* masks q_pos - k_pos > window_left;  -1 = off (window_size_left)  */
+    int window_right;         /* masks k_pos - q_pos > window_right; -1 = off (window_size_right) */
+    const float* alibi_slopes;/* device fp32 [heads] or NULL; score -= slope*|q_pos-k_pos|
+                                 (alibi_slopes_ptr; subtracts, as src/flash_forward.h:173) */
+    float p_dropout;          /* in [0,1)                                (param.dropout_prob) */
+    uint64_t seed;            /* Philox key                 (seed of init_curand_states)      */
+    uint64_t offset;          /* draws skipped at the start of every stream (0 = first launch) */
+    uint64_t unit0;           /* global b*H+h index of this call's first (batch, head) unit:
+                                 keeps the dropout mask independent of how units are sharded  */
+    int num_splits;           /* 0 = fa_num_splits_heuristic with the device's SM count,
+                                 1 = no split, n = forced                  (param.split_num) */
+    int64_t q_pos0, k_pos0;   /* global position of query row 0 / key column 0 (0 = reference
+                                 behaviour; used to run one block of a sharded sequence)      */
+    void* workspace;          /* device; split partials (param.O_tmp, param.L, param.M) */
+    size_t workspace_bytes;
+    int* status;              /* device int or NULL: set non-zero if a device wait timed out */
+    void* stream;             /* cudaStream_t; NULL = default stream (the reference's)       */
+} fa_fwd_params;
+
+/* Forward pass: O = dropout(softmax(scale*Q K^T - slope*|i-j| + masks)) V, LSE.
+ * Replaces the launches of forward_kernel (src/flash_forward.h:13-306),
+ * forward_kernel_splitkv + forward_kernel_splitkv_combine
+ * (src/flash_forward_splitkv.h:14-399) and init_curand_states
+ * (src/init_curand_states.h:7-14) issued by src/main.cu:128-205.
+ * Asynchronous on p->stream. */
+int fa_fwd(const fa_fwd_params* p);
+
+/* Bytes of workspace fa_fwd needs for p (0 when it will not split).
+ * Replaces the cudaMalloc sizing of O_tmp/L/M at src/main.cu:160-162. */
+size_t fa_fwd_workspace_bytes(const fa_fwd_params* p);
+
+/* Split count fa_fwd will use for p (resolves num_splits == 0). */
+int fa_fwd_resolve_splits(const fa_fwd_params* p);
+
+/* The reference's split policy, same arguments and result as
+ * num_splits_heuristic (src/main.cu:391-422). */
+int fa_num_splits_heuristic(int batch_nheads_mblocks, int num_sms, int num_n_blocks, int max_splits,
+                            int seq_len);
+
+/* Writes the dropout keep-mask fa_fwd applies for p (1 = kept, 0 = dropped) to
+ * keep[B,H,Nq,Nk] (device, uint8).  The reference cannot show its mask; this is
+ * the check that the stateless generator reproduces src/flash_forward.h:221-237. */
+int fa_dropout_mask(const fa_fwd_params* p, uint8_t* keep);
+
+/* Merges a partial result into an accumulated one, row by row:
+ *   lse' = log(exp(lse_acc) + exp(lse_part)),
+ *   o'   = exp(lse_acc-lse') o_acc + exp(lse_part-lse') o_part.
+ * o_acc fp32 [rows, head_dim], o_part of part_dtype.  The same algebra as
+ * forward_kernel_splitkv_combine (src/flash_forward_splitkv.h:359-397), used to
+ * chain the blocks of a sequence sharded across GPUs. */
+int fa_merge_partial(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part,
+                     int part_dtype, int64_t rows, int head_dim, void* stream);
+
+/* Casts the fp32 accumulator of fa_merge_partial to the 16-bit output type. */
+int fa_cast_output(const float* o_acc, void* o, int o_dtype, int64_t elems, void* stream);
+
+/* Host-buffer forward, the path the reference's main() takes around its kernel
+ * (cudaMemcpy H2D src/main.cu:105-107, launch, cudaMemcpy D2H :219): q/k/v/o/lse
+ * and alibi_slopes in *p are HOST pointers (pinned memory overlaps best).  Device
+ * staging buffers are allocated on first use and cached per device; copies and
+ * kernels are pipelined over (batch, head) slices.  Synchronous. */
+int fa_fwd_host(const fa_fwd_params* p);
+/* Frees the staging buffers fa_fwd_host cached. */
+void fa_fwd_host_release(void);
+
+/* Message for a return code. */
+const char* fa_strerror(int code);
+int fa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H */

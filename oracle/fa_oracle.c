@@ -102,6 +102,9 @@ int fa_oracle_dropout_keep(const fa_oracle_dropout_geom* g, int b, int h, int64_
         int64_t w = (g->q_pos0 + rb * TILE - g->window_left - g->k_pos0) / TILE;
         nbmin = imax64(nbmin, imax64(0, w));
     }
+    /* tiles left of the window are never visited by the CTA: nothing is drawn
+     * for them (and every element there is masked anyway) */
+    if (cb < nbmin) return 1;
     /* one stream per CTA: flash_forward.h:52 with grid (Tr*splits, H, B) */
     const uint64_t subseq = ((uint64_t)b * g->heads + h) * (uint64_t)(Tr * splits) + (uint64_t)(rb * splits + s);
     /* 64 draws per KV tile in c_frag[i][j] order (flash_forward.h:223-227); the
