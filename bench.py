@@ -91,7 +91,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -100,7 +100,16 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def wait_first_sample(self, limit=10.0):
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.lines and time.perf_counter() - t0 < limit:
+            time.sleep(0.01)
+
+    def mark(self):
+        """Samples taken before this call (warm-up) are not counted."""
+        self.t_mark = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
@@ -108,7 +117,10 @@ class ClockSampler:
         self.proc.terminate()
         self.thread.join(timeout=2)
         sm, smax, reasons = [], None, set()
-        for ln in self.lines:
+        t_mark = getattr(self, "t_mark", 0.0)
+        for t, ln in self.lines:
+            if t < t_mark:
+                continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -223,7 +235,7 @@ def make_inputs(torch, w, seed, device, copies):
     return sets
 
 
-def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier):
+def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier, sampler=None):
     """Device-timed steps: returns seconds per step (this rank)."""
     units = w["B"] * w["H"]
     dev = sets[0][0].device
@@ -243,6 +255,8 @@ def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier):
         step(i)
     barrier()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
@@ -294,7 +308,7 @@ def time_e2e(torch, fa, w, steps, warmup, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -344,7 +358,8 @@ def main():
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
     if sampler:
         sampler.start()
-    sec = time_device(torch, fa, name, w, sets, args.steps, args.warmup, rank, barrier)
+        sampler.wait_first_sample()
+    sec = time_device(torch, fa, name, w, sets, args.steps, args.warmup, rank, barrier, sampler)
     clocks = sampler.stop() if sampler else None
     sec = max_over_ranks(sec)
     del sets
