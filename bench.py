@@ -314,6 +314,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-secondary", action="store_true", help="skip the c3/c4 side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -365,8 +366,11 @@ def main():
     del sets
     torch.cuda.empty_cache()
 
-    e2e_sec, h2d, d2h = time_e2e(torch, fa, w, max(3, min(args.steps, 10)), 2, rank)
-    e2e_sec = max_over_ranks(e2e_sec)
+    if args.no_e2e:
+        e2e_sec, h2d, d2h = float("inf"), 0, 0
+    else:
+        e2e_sec, h2d, d2h = time_e2e(torch, fa, w, max(3, min(args.steps, 10)), 2, rank)
+        e2e_sec = max_over_ranks(e2e_sec)
 
     is_decode = name == "c4"
     if is_decode:
