@@ -14,7 +14,7 @@ FA_OK = 0
 #: every symbol include/fa_b200.h declares
 EXPORTS = ["fa_fwd", "fa_fwd_workspace_bytes", "fa_fwd_resolve_splits", "fa_num_splits_heuristic",
            "fa_dropout_mask", "fa_merge_partial", "fa_cast_output", "fa_fwd_host", "fa_fwd_host_release",
-           "fa_strerror", "fa_version"]
+           "fa_fwd_static_scratch", "fa_static_scratch_bytes", "fa_strerror", "fa_version"]
 
 
 class FwdParams(ctypes.Structure):
@@ -65,6 +65,10 @@ def load():
     L.fa_fwd_host.restype = ctypes.c_int
     L.fa_fwd_host_release.argtypes = []
     L.fa_fwd_host_release.restype = None
+    L.fa_fwd_static_scratch.argtypes = [pp]
+    L.fa_fwd_static_scratch.restype = ctypes.c_int
+    L.fa_static_scratch_bytes.argtypes = []
+    L.fa_static_scratch_bytes.restype = ctypes.c_size_t
     L.fa_fwd_workspace_bytes.argtypes = [pp]
     L.fa_fwd_workspace_bytes.restype = ctypes.c_size_t
     L.fa_fwd_resolve_splits.argtypes = [pp]

@@ -127,6 +127,35 @@ int fa_fwd_host(const fa_fwd_params* p);
 /* Frees the staging buffers fa_fwd_host cached. */
 void fa_fwd_host_release(void);
 
+/* Size of the built-in scratch of fa_fwd_static_scratch. */
+#define FA_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* fa_fwd for callers that cannot allocate device memory -- a process whose GPU
+ * memory is wholly owned by another allocator, a plugin that may not call
+ * cudaMalloc, a latency-critical loop -- and therefore cannot provide
+ * p->workspace for a split launch.  No counterpart in the reference, which
+ * cudaMallocs its split buffers before every run (src/main.cu:160-162).
+ *
+ * Same arguments and results as fa_fwd, except that p->workspace and
+ * p->workspace_bytes are ignored: the split partials go to a fixed
+ * FA_STATIC_SCRATCH_BYTES (32 MiB) array in device global memory that belongs to
+ * the library image (each GPU that loads the library holds it until exit).
+ * Launches whose partials need more return FA_ERR_TOO_LARGE; the need is what
+ * fa_fwd_workspace_bytes reports (batch*heads*splits*seqlen_q*(head_dim+1)*4
+ * bytes, rounded up to 256).  Config 4 of the baseline (2048 units, 16 splits,
+ * one query row, head_dim 128) needs 16.1 MiB.
+ *
+ * The call itself allocates nothing and calls no allocating routine.  The first
+ * call on each device looks up the array's device address
+ * (cudaGetSymbolAddress) and keeps it; make that first call outside any stream
+ * capture.  All calls on a device share the one array, which keeps whatever
+ * the last call left: nothing in it needs clearing (every partial that is read
+ * is written first by the same call), but two calls that overlap on the GPU --
+ * different streams, or different host threads -- race on it and give wrong
+ * results.  Serialise them, or use fa_fwd with separate workspaces. */
+int fa_fwd_static_scratch(const fa_fwd_params* p);
+size_t fa_static_scratch_bytes(void);
+
 /* Message for a return code. */
 const char* fa_strerror(int code);
 int fa_version(void);
