@@ -2,47 +2,77 @@
 // forward_kernel (src/flash_forward.h:13-306) and forward_kernel_splitkv
 // (src/flash_forward_splitkv.h:14-344).
 //
-// One CTA owns one 128-row query tile of one (batch, head) unit, optionally one
-// KV split of it, exactly the reference's work decomposition (grid
-// (Tr*splits, H, B), src/main.cu:142-158).  Inside the CTA the roles are split by warp:
-//   warps 0-3  softmax: thread r owns query row r.  S is read from tensor memory
-//              (tcgen05.ld), masked / biased / exponentiated in registers, the
-//              16-bit P is written back to tensor memory over S (tcgen05.st), and
-//              the running (max, sum) and the lazy rescale of O live here.
-//   warp 4     TMA producer: streams the Q tile once and K/V tiles through an
-//              mbarrier ring (cp.async.bulk.tensor, 128-byte swizzle).
-//   warp 5     MMA issuer: one thread issues tcgen05.mma for S = Q K^T (both
-//              operands in shared memory) and O += P V (P in tensor memory, V in
-//              shared memory, MN-major), with accumulators in tensor memory.
+// A CTA owns NQ (1 or 2) consecutive 128-row query tiles of one (batch, head)
+// unit, optionally one KV split of them; each query tile is exactly one CTA of
+// the reference's decomposition (grid (Tr*splits, H, B), src/main.cu:142-158),
+// which is what the dropout streams are keyed on.  Roles by warp:
+//   softmax groups (4 warps per query tile): thread r owns query row r.  S is read
+//       from tensor memory (tcgen05.ld), masked / biased / exponentiated in
+//       registers, the 16-bit P is written back to tensor memory over S
+//       (tcgen05.st); the running (max, sum) and the lazy rescale of O live here.
+//   TMA producer warp: streams the Q tiles once and K/V tiles through an mbarrier
+//       ring (cp.async.bulk.tensor, 128-byte swizzle).
+//   MMA issuer warp: one thread issues tcgen05.mma for S_i = Q_i K^T (operands in
+//       shared memory) and O_i += P_i V (P in tensor memory, V in shared memory,
+//       MN-major), accumulators in tensor memory.  With NQ = 2 the two query tiles
+//       alternate on the tensor pipe, so the softmax of one overlaps the MMAs of
+//       the other while both share every K/V tile brought in by TMA.
 // The reference keeps O in shared memory and renormalises it every tile
 // (src/flash_forward.h:248-290); here O stays un-normalised in tensor memory and
-// is divided by the row sum once, in the epilogue.  Two CTAs are resident per SM
-// (256 TMEM columns, <= 97 KB shared memory each) so that one CTA's softmax
-// overlaps the other's tensor-core work.
+// is divided by the row sum once, in the epilogue.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_runtime.h>
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
+
+// Optional timeline tracing for kernel development (compiled out unless FA_TRACE is
+// defined): lane 0 of every warp of CTA 0 records (event, clock) pairs.
+#ifdef FA_TRACE
+__device__ long long fa_trace_buf[16 * 512];
+extern "C" int fa_trace_read(long long* host_out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_trace_buf, sizeof(long long) * 16 * 512));
+}
+#define FA_TR(ev)                                                                              \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 255) {                        \
+            fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n] = (ev);                          \
+            fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n + 1] = clock64();                 \
+            ++tr_n;                                                                            \
+        }                                                                                      \
+    } while (0)
+#else
+#define FA_TR(ev) do { } while (0)
+#endif
 
 namespace fa {
 
 namespace {
 
-constexpr int kThreads = 192;
-constexpr int kSoftmaxThreads = 128;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by > 2^8
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
 
-template <int D>
+template <int D, int NQ>
 struct Cfg {
-    static constexpr int kStages = (D == 64) ? 2 : 1;
-    static constexpr int kBoxes = D / 64;              // 64-element (128-byte) column blocks per tile
-    static constexpr int kTileBytes = kTile * D * 2;   // one Q, K or V tile
-    static constexpr int kTmemCols = 256;              // S: [0,128)  (P aliases [0,64));  O: [128,128+D)
+    // NQ = 2 rounds the helper warps up to a full warpgroup so that registers can be
+    // moved from it to the softmax warpgroups (setmaxnreg works on whole warpgroups).
+    static constexpr int kThreads = NQ == 2 ? 384 : 192;
+    static constexpr int kRegsHelper = 48;    // producer / MMA warpgroup after the hand-over
+    static constexpr int kRegsSoftmax = 224;  // softmax warpgroups after the hand-over
+    static constexpr int kProducerWarp = NQ * 4;
+    static constexpr int kMmaWarp = NQ * 4 + 1;
+    static constexpr int kStages = (D == 64) ? (NQ == 2 ? 3 : 2) : (NQ == 2 ? 2 : 1);
+    static constexpr int kBoxes = D / 64;             // 64-element (128-byte) column blocks per tile
+    static constexpr int kTileBytes = kTile * D * 2;  // one Q, K or V tile
+    // TMEM columns: S_i at i*128 (P_i aliases S_i[0,64)); O_i after the S blocks.
+    static constexpr int kTmemCols = NQ == 2 ? 512 : 256;
+    static constexpr int kTmemO = NQ * kTile;
     static constexpr int kSmemQ = 0;
-    static constexpr int kSmemK = kTileBytes;
+    static constexpr int kSmemK = NQ * kTileBytes;
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
     static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-    static constexpr int kNumBars = 4 + 4 * kStages;
+    static constexpr int kNumBars = 1 + 3 * NQ + 4 * kStages;
     static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
 };
 
@@ -51,6 +81,7 @@ struct TileRange {
 };
 
 __device__ __forceinline__ TileRange kv_tile_range(const FwdArgs& a, int rb, int split) {
+    if (rb >= a.tr) return {0, 0};
     const long long q0 = a.q_pos0 + static_cast<long long>(rb) * kTile;
     int lo = 0, hi = a.tc;
     if (a.num_splits > 1) {  // src/flash_forward_splitkv.h:40-43
@@ -69,6 +100,7 @@ __device__ __forceinline__ TileRange kv_tile_range(const FwdArgs& a, int rb, int
         const long long last = q0 + kTile - 1 - a.k_pos0;
         hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
     }
+    if (hi < lo) hi = lo;
     return {lo, hi};
 }
 
@@ -89,11 +121,83 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-template <int D, bool kBf16, bool kAlibi, bool kDropout>
-__global__ void __launch_bounds__(kThreads, 2)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// One lane polls, then every lane observes the completed phase itself.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    return __all_sync(0xffffffffu, ok) != 0;
+}
+
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// Eight (D = 128) or four (D = 64) back-to-back MMAs of one S = Q K^T tile in a single
+// asm block: the descriptors differ only in the low word (start address, 16-byte units),
+// which is stepped inside the block, so the issuing thread does no other work between MMAs.
+// Steps for a [128 x D] tile stored as 64-column boxes: 32 bytes per k-step inside a box
+// (+2 units), next box after four steps (16 KB further: +1024 - 6 units).
+#define FA_QK_STEP(inc)                                                                        \
+    "add.u32 qa, qa, " #inc ";\n\tadd.u32 kb, kb, " #inc ";\n\t"                                 \
+    "mov.b64 da, {qa, %3};\n\tmov.b64 db, {kb, %3};\n\t"                                        \
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t"
+#define FA_QK_HEAD                                                                             \
+    "{\n\t.reg .pred p0, p1;\n\t.reg .b32 qa, kb;\n\t.reg .b64 da, db;\n\t"                       \
+    "setp.ne.b32 p0, 0, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"                                        \
+    "mov.b32 qa, %1;\n\tmov.b32 kb, %2;\n\t"                                                    \
+    "mov.b64 da, {qa, %3};\n\tmov.b64 db, {kb, %3};\n\t"                                        \
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p0;\n\t"
+template <int D>
+__device__ __forceinline__ void issue_qk_block(uint32_t d_tmem, uint32_t qa_lo, uint32_t kb_lo, uint32_t desc_hi,
+                                               uint32_t idesc) {
+    if constexpr (D == 128) {
+        asm volatile(FA_QK_HEAD FA_QK_STEP(2) FA_QK_STEP(2) FA_QK_STEP(2) FA_QK_STEP(1018) FA_QK_STEP(2)
+                         FA_QK_STEP(2) FA_QK_STEP(2) "}"
+                     ::"r"(d_tmem), "r"(qa_lo), "r"(kb_lo), "r"(desc_hi), "r"(idesc)
+                     : "memory");
+    } else {
+        asm volatile(FA_QK_HEAD FA_QK_STEP(2) FA_QK_STEP(2) FA_QK_STEP(2) "}"
+                     ::"r"(d_tmem), "r"(qa_lo), "r"(kb_lo), "r"(desc_hi), "r"(idesc)
+                     : "memory");
+    }
+}
+
+// Eight back-to-back MMAs of O += P V over the 128 keys of a tile: P advances 8 TMEM
+// columns (16 packed elements) and V 16 rows (2048 bytes = 128 descriptor units) per step.
+#define FA_PV_STEP                                                                             \
+    "add.u32 pa, pa, 8;\n\tadd.u32 vb, vb, 128;\n\tmov.b64 db, {vb, %3};\n\t"                    \
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p1;\n\t"
+__device__ __forceinline__ void issue_pv_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
+                                               uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p0, p1;\n\t.reg .b32 pa, vb;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p0, %5, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
+        "mov.b32 pa, %1;\n\tmov.b32 vb, %2;\n\tmov.b64 db, {vb, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p0;\n\t"
+        FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(vb_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
+__global__ void __launch_bounds__(Cfg<D, NQ>::kThreads, NQ == 1 ? 2 : 1)
 fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
-    using C = Cfg<D>;
+    using C = Cfg<D, NQ>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles need a 1024-byte aligned base
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -104,36 +208,51 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t bar0 = smem_base + C::kSmemBar;
     // barrier map
     const uint32_t bar_q_full = bar0;
-    const uint32_t bar_s_full = bar0 + 8;
-    const uint32_t bar_p_full = bar0 + 16;
-    const uint32_t bar_o_full = bar0 + 24;
-    const uint32_t bar_k_full = bar0 + 32;                      // [kStages]
-    const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;   // [kStages]
-    const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;   // [kStages]
-    const uint32_t bar_v_empty = bar_v_full + 8 * C::kStages;   // [kStages]
+    const uint32_t bar_s_full = bar0 + 8;                        // [NQ]
+    const uint32_t bar_p_full = bar_s_full + 8 * NQ;             // [NQ]
+    const uint32_t bar_o_full = bar_p_full + 8 * NQ;             // [NQ]
+    const uint32_t bar_k_full = bar_o_full + 8 * NQ;             // [kStages]
+    const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;    // [kStages]
+    const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;    // [kStages]
+    const uint32_t bar_v_empty = bar_v_full + 8 * C::kStages;    // [kStages]
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kSmemBar + 8 * C::kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kSmemBar + 8 * C::kNumBars + 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef FA_TRACE
+    int tr_n = 0;
+#endif
 
-    // ---- which tile is this CTA ------------------------------------------------
-    const int per_unit = a.tr * a.num_splits;
+    // ---- which query tiles does this CTA own ------------------------------------
+    const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
+    const int per_unit = trq * a.num_splits;
     const int unit = blockIdx.x / per_unit;
     const int bx = blockIdx.x - unit * per_unit;
     const int split = bx % a.num_splits;
-    int rb = bx / a.num_splits;
-    if (a.is_causal) rb = a.tr - 1 - rb;  // heaviest query tiles first
-    const TileRange range = kv_tile_range(a, rb, split);
-    const int n_tiles = range.hi - range.lo;
+    int qb = bx / a.num_splits;
+    if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
+    TileRange range[NQ];
+    int lo = 0x7fffffff, hi = 0;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+        range[i] = kv_tile_range(a, qb * NQ + i, split);
+        if (range[i].hi > range[i].lo) {
+            lo = min(lo, range[i].lo);
+            hi = max(hi, range[i].hi);
+        }
+    }
+    const int n_union = hi > lo ? hi - lo : 0;  // KV tiles streamed by this CTA: [lo, hi)
 
     // ---- set-up ----------------------------------------------------------------
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar_q_full, 1);
-        mbar_init(bar_s_full, 1);
-        mbar_init(bar_p_full, kSoftmaxThreads);
-        mbar_init(bar_o_full, 1);
+        for (int i = 0; i < NQ; ++i) {
+            mbar_init(bar_s_full + 8 * i, 1);
+            mbar_init(bar_p_full + 8 * i, 128);
+            mbar_init(bar_o_full + 8 * i, 1);
+        }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(bar_k_full + 8 * s, 1);
             mbar_init(bar_k_empty + 8 * s, 1);
@@ -142,11 +261,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         mbar_fence_init();
     }
-    if (warp == 5 && n_tiles > 0) {
+    if (warp == C::kMmaWarp && n_union > 0) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == C::kProducerWarp && lane == 0) {
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
@@ -154,136 +273,227 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem_base = (n_tiles > 0) ? *tmem_slot : 0u;
-    const uint32_t tmem_s = tmem_base;          // S accumulator, 128 fp32 columns
-    const uint32_t tmem_p = tmem_base;          // P (16-bit, two per column) over S[0,64)
-    const uint32_t tmem_o = tmem_base + kTile;  // O accumulator, D fp32 columns
+    const uint32_t tmem_base = (n_union > 0) ? *tmem_slot : 0u;
 
     int fail = 0;
 
-    if (n_tiles > 0 && warp == 4) {
-        // ======================= TMA producer ===================================
-        if (lane == 0) {
-            mbar_expect_tx(bar_q_full, C::kTileBytes);
+    // With NQ = 2 the 384 threads start with 168 registers each; the helper warpgroup
+    // (producer, MMA issuer, two idle warps) hands most of its share to the two softmax
+    // warpgroups, which hold a 128-column score row per thread.  Each register regime
+    // covers one whole branch below.
+    if (warp >= NQ * 4) {
+        if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsHelper));
+        if (n_union > 0 && warp == C::kProducerWarp) {
+            // ======================= TMA producer ===================================
+            if (lane == 0) {
+                int q_tiles = 0;
 #pragma unroll
-            for (int b = 0; b < C::kBoxes; ++b)
-                tma_load_3d(sQ + b * (kTile * 128), &tmap_q, bar_q_full, b * 64, rb * kTile, unit);
-            for (int j = 0; j < n_tiles; ++j) {
-                const int st = j % C::kStages;
-                const uint32_t ph = (j / C::kStages) & 1;
-                const int row = (range.lo + j) * kTile;
-                if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
-                mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
+                for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
+                mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
 #pragma unroll
-                for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, unit);
-                if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
-                mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
+                for (int i = 0; i < NQ; ++i) {
+                    if (range[i].hi > range[i].lo) {
 #pragma unroll
-                for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, unit);
-            }
-        }
-    } else if (n_tiles > 0 && warp == 5) {
-        // ======================= MMA issuer =====================================
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = make_idesc_f16(kTile, kTile, kBf16, false);
-            constexpr uint32_t idesc_pv = make_idesc_f16(kTile, D, kBf16, true);
-            auto issue_qk = [&](int st) {
-                // S = Q K^T: K-dimension = head_dim, 16 elements (32 bytes) per instruction
-#pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = (ks / 4) * (kTile * 128) + (ks % 4) * 32;
-                    umma_ss(tmem_s, make_smem_desc(sQ + off, 0, 1024),
-                            make_smem_desc(sK + st * C::kTileBytes + off, 0, 1024), idesc_qk, ks > 0);
-                }
-            };
-            do {
-                if (!mbar_wait(bar_q_full, 0, abort_flag)) { fail = 3; break; }
-                if (!mbar_wait(bar_k_full, 0, abort_flag)) { fail = 4; break; }
-                tc_fence_after_sync();
-                issue_qk(0);
-                umma_commit(bar_k_empty);
-                umma_commit(bar_s_full);
-                for (int j = 0; j < n_tiles; ++j) {
-                    const int st = j % C::kStages;
-                    const uint32_t ph = (j / C::kStages) & 1;
-                    if (!mbar_wait(bar_p_full, j & 1, abort_flag)) { fail = 5; break; }
-                    if (!mbar_wait(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
-                    tc_fence_after_sync();
-                    // O += P V: K-dimension = 128 keys, 16 per instruction = 8 TMEM columns of P and
-                    // 16 rows (2048 bytes) of V; the two 64-wide halves of V are 16 KB apart.
-#pragma unroll
-                    for (int ks = 0; ks < kTile / 16; ++ks)
-                        umma_ts(tmem_o, tmem_p + ks * 8,
-                                make_smem_desc(sV + st * C::kTileBytes + ks * 2048, kTile * 128, 1024), idesc_pv,
-                                (j > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(bar_v_empty + 8 * st);
-                    if (j + 1 < n_tiles) {
-                        const int st1 = (j + 1) % C::kStages;
-                        const uint32_t ph1 = ((j + 1) / C::kStages) & 1;
-                        if (!mbar_wait(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
-                        tc_fence_after_sync();
-                        issue_qk(st1);
-                        umma_commit(bar_k_empty + 8 * st1);
-                        umma_commit(bar_s_full);
-                    } else {
-                        umma_commit(bar_o_full);
+                        for (int b = 0; b < C::kBoxes; ++b)
+                            tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
+                                        (qb * NQ + i) * kTile, unit);
                     }
                 }
-            } while (false);
+                for (int t = 0; t < n_union; ++t) {
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int row = (lo + t) * kTile;
+                    if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
+                    FA_TR(10);
+                    mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, unit);
+                    if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
+                    FA_TR(11);
+                    mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, unit);
+                }
+            }
+        } else if (n_union > 0 && warp == C::kMmaWarp) {
+            // ======================= MMA issuer =====================================
+            if (elect_one()) {
+                constexpr uint32_t idesc_qk = make_idesc_f16(kTile, kTile, kBf16, false);
+                constexpr uint32_t idesc_pv = make_idesc_f16(kTile, D, kBf16, true);
+                // Descriptor words.  High word: SBO = 1024, 128-byte swizzle, version 1; low word:
+                // start address (and for V the LBO of 16 KB between its two 64-column halves).
+                const uint64_t dqk = make_smem_desc(0, 0, 1024);
+                const uint64_t dvv = make_smem_desc(0, kTile * 128, 1024);
+                const uint32_t desc_hi = static_cast<uint32_t>(dqk >> 32);
+                const uint32_t q_lo = static_cast<uint32_t>(dqk) | (sQ >> 4);
+                const uint32_t k_lo = static_cast<uint32_t>(dqk) | (sK >> 4);
+                const uint32_t v_lo = static_cast<uint32_t>(dvv) | (sV >> 4);
+                auto issue_qk = [&](int i, int st) {
+                    issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
+                                      k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
+                };
+                auto issue_pv = [&](int i, int st, uint32_t accumulate) {
+                    issue_pv_block(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
+                                   v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv, accumulate);
+                };
+                auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
+                do {
+                    if (!mbar_wait(bar_q_full, 0, abort_flag)) { fail = 3; break; }
+                    if (!mbar_wait(bar_k_full, 0, abort_flag)) { fail = 4; break; }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int i = 0; i < NQ; ++i) {
+                        if (active(i, lo)) {
+                            issue_qk(i, 0);
+                            umma_commit(bar_s_full + 8 * i);
+                        }
+                    }
+                    umma_commit(bar_k_empty);
+                    for (int t = 0; t < n_union && fail == 0; ++t) {
+                        const int tile = lo + t;
+                        const int st = t % C::kStages;
+                        const uint32_t ph = (t / C::kStages) & 1;
+                        const int st1 = (t + 1) % C::kStages;
+                        const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
+                        const bool more = t + 1 < n_union;
+                        if (!mbar_wait(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
+                        FA_TR(20);
+                        bool k_ready = false;
+#pragma unroll
+                        for (int i = 0; i < NQ; ++i) {
+                            if (active(i, tile)) {
+                                if (!mbar_wait(bar_p_full + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
+                                FA_TR(21 + 10 * i);
+                                tc_fence_after_sync();
+                                issue_pv(i, st, tile > range[i].lo ? 1u : 0u);
+                                if (tile == range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
+                                FA_TR(22 + 10 * i);
+                            }
+                            if (more && active(i, tile + 1)) {
+                                if (!k_ready) {
+                                    if (!mbar_wait(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
+                                    FA_TR(23);
+                                    tc_fence_after_sync();
+                                    k_ready = true;
+                                }
+                                issue_qk(i, st1);
+                                umma_commit(bar_s_full + 8 * i);
+                                FA_TR(24 + 10 * i);
+                            }
+                        }
+                        if (fail) break;
+                        umma_commit(bar_v_empty + 8 * st);
+                        if (more) umma_commit(bar_k_empty + 8 * st1);
+                    }
+                } while (false);
+            }
         }
-    } else if (warp < 4) {
+    } else {
+        if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
         // ======================= softmax / epilogue =============================
-        const int r = threadIdx.x;                       // row inside the tile
+        const int qi = warp >> 2;                        // which query tile of the CTA
+        const int rb = qb * NQ + qi;                     // its 128-row block inside the unit
+        const int r = threadIdx.x & 127;                 // row inside the tile
         const int row = rb * kTile + r;                  // row inside the unit
         const long long qpos = a.q_pos0 + row;
-        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        const TileRange mine_r = (qi == 0) ? range[0] : range[NQ - 1];
+        const int t_lo = mine_r.lo;
+        const int n_tiles = mine_r.hi - mine_r.lo;
+        const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+        const uint32_t tmem_s = tmem_base + qi * kTile;          // S accumulator, 128 fp32 columns
+        const uint32_t tmem_p = tmem_s;                          // P (16-bit, two per column) over S[0,64)
+        const uint32_t tmem_o = tmem_base + C::kTmemO + qi * D;  // O accumulator, D fp32 columns
+        const uint32_t my_s_full = bar_s_full + 8 * qi;
+        const uint32_t my_p_full = bar_p_full + 8 * qi;
+        const uint32_t my_o_full = bar_o_full + 8 * qi;
         float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
         float l_sum = 0.0f;
         float slope2 = 0.0f;
-        if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * 1.4426950408889634f;
+        if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
+        // every unmasked key lies at or before the query: |q - k| = q - k
+        const bool keys_not_after = a.is_causal || a.window_right == 0;
         unsigned long long subseq = 0;
         if constexpr (kDropout)
-            subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(per_unit) +
+            subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
                      static_cast<unsigned long long>(rb * a.num_splits + split);
+        const float scale2 = a.scale_log2;
+        // Dropout keep bits of this row for KV tile j of this query tile: bit 2*g + w <-> columns
+        // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
+        // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
+        // tile ahead, while the warp would otherwise wait for S.
+        auto tile_keep_bits = [&](int j) -> uint32_t {
+            if constexpr (!kDropout) return 0xffffffffu;
+            uint32_t mine = 0;
+            if (lane < 16) mine = philox_keep4(a.drop, subseq, 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
+            const int half = (lane >> 3) & 1;
+            uint32_t bits = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
+            return bits;
+        };
+        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(0) : 0u;
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int cb = range.lo + j;
+            const int cb = t_lo + j;
             const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
-            // the TMEM loads below are warp-collective: decide as a warp
-            if (!__all_sync(0xffffffffu, mbar_wait(bar_s_full, j & 1, abort_flag))) { fail = 8; break; }
+            FA_TR(1);
+            if (!mbar_wait_warp(my_s_full, j & 1, abort_flag)) { fail = 8; break; }
+            FA_TR(2);
             tc_fence_after_sync();
 
-            uint32_t sr[4][32];
+            float s[128];
+            {
+                uint32_t tmp[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_base + c * 32, sr[c]);
-            tmem_wait_ld();
+                for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_base + c * 32, tmp[c]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 128; ++c) s[c] = __uint_as_float(tmp[c / 32][c % 32]);
+            }
+            FA_TR(3);
 
             // columns this row may attend to inside the tile: [c_lo, c_hi]
             int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
             if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
             if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
             if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
-            const bool need_mask = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
+            if (__any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1)) {
+#pragma unroll
+                for (int c = 0; c < 128; ++c)
+                    if (c < c_lo || c > c_hi) s[c] = -INFINITY;
+            }
 
-            // scaled (and biased) scores in log2 units, and the tile max
-            float m_tile = -INFINITY;
-            const float dist0 = static_cast<float>(qpos - kbase);
+            // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
+            // (softmax_scale > 0) and the scale is folded into the exponent's FMA.
+            float m_tile;
+            if constexpr (kAlibi) {
+                const float dist0 = static_cast<float>(qpos - kbase);
+                if (keys_not_after) {
+                    const float base = -slope2 * dist0;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 128; ++c) s[c] = fmaf(s[c], scale2, fmaf(slope2, static_cast<float>(c), base));
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(sr[c][i]) * a.scale_log2;
-                    if constexpr (kAlibi) s = fmaf(-slope2, fabsf(dist0 - static_cast<float>(c * 32 + i)), s);
-                    if (need_mask) {
-                        const int col = c * 32 + i;
-                        if (col < c_lo || col > c_hi) s = -INFINITY;
-                    }
-                    sr[c][i] = __float_as_uint(s);
-                    m_tile = fmaxf(m_tile, s);
+                    for (int c = 0; c < 128; ++c) s[c] = fmaf(-slope2, fabsf(dist0 - static_cast<float>(c)), s[c] * scale2);
                 }
             }
+            {
+                float mx[4] = {s[0], s[1], s[2], s[3]};
+#pragma unroll
+                for (int c = 4; c < 128; c += 8) {
+                    mx[0] = max3(mx[0], s[c], s[c + 1]);
+                    mx[1] = max3(mx[1], s[c + 2], s[c + 3]);
+                    if (c + 4 < 128) {
+                        mx[2] = max3(mx[2], s[c + 4], s[c + 5]);
+                        mx[3] = max3(mx[3], s[c + 6], s[c + 7]);
+                    }
+                }
+                m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                if constexpr (!kAlibi) m_tile *= scale2;
+            }
+            FA_TR(4);
 
             // lazy rescale: keep the old reference max unless the new one is much larger
             float m_new = m_ref;
@@ -294,7 +504,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             const bool rescale = (j > 0) && (m_new != m_ref);
             if (__any_sync(0xffffffffu, rescale)) {
-                // PV of the previous tile has completed (its commit precedes s_full), so O is stable.
+                // P V of the previous tile has completed (its commit precedes s_full), so O is stable.
                 const float f = rescale ? factor : 1.0f;
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
@@ -308,59 +518,58 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             l_sum *= (m_new != m_ref) ? factor : 1.0f;
             m_ref = m_new;
-            const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
+            const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            const uint32_t keep_bits = keep_next;
+            FA_TR(5);
 
-            // dropout keep bits of this row for the tile: bit 4*i + w <-> 16-column block i,
-            // w = 2*((col%16)/8) + col%2
-            uint32_t keep_bits = 0xffffffffu;
-            if constexpr (kDropout) {
-                const unsigned long long tile_first = 64ull * static_cast<unsigned long long>(j);
-                uint32_t mine = 0;
-                if (lane < 16)  // lane = 2*i + row-half: draws 8*i + 4*half + {0..3}
-                    mine = philox_keep4(a.drop, subseq, tile_first + 4ull * lane);
-                const int half = (lane >> 3) & 1;
-                keep_bits = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) keep_bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
-            }
-
-            // P = exp2(s - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
-            float acc = 0.0f;
+            // P = exp2(s*scale - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
+            float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            const float2 neg_m2 = make_float2(neg_m, neg_m);
+            const float2 scale22 = make_float2(scale2, scale2);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t pr[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int col = c * 64 + 2 * i;
-                    const float p0 = fast_exp2(__uint_as_float(sr[col / 32][col % 32]) - m_use);
-                    const float p1 = fast_exp2(__uint_as_float(sr[(col + 1) / 32][(col + 1) % 32]) - m_use);
-                    acc += p0 + p1;
-                    uint32_t packed = pack2<kBf16>(p0, p1);
+                for (int g = 0; g < 8; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
+                    uint32_t msk = 0xffffffffu;
                     if constexpr (kDropout) {
-                        const uint32_t nib = keep_bits >> (4 * (col / 16) + 2 * ((col % 16) / 8));
-                        const uint32_t msk = ((nib & 1u) ? 0x0000ffffu : 0u) | ((nib & 2u) ? 0xffff0000u : 0u);
-                        packed &= msk;
+                        const uint32_t two = (keep_bits >> (2 * (c * 8 + g))) & 3u;
+                        msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
                     }
-                    pr[i] = packed;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int col = c * 64 + g * 8 + q * 2;
+                        float2 x = make_float2(s[col], s[col + 1]);
+                        if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
+                        else x = __ffma2_rn(x, scale22, neg_m2);
+                        float2 p;
+                        p.x = fast_exp2(x.x);
+                        p.y = fast_exp2(x.y);
+                        acc[q] = __fadd2_rn(acc[q], p);
+                        pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
+                    }
                 }
                 tmem_st32(tmem_p + lane_base + c * 32, pr);
             }
-            l_sum += acc;
+            FA_TR(6);
+            l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(bar_p_full);
+            mbar_arrive(my_p_full);
+            FA_TR(7);
+            if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
         }
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
         bool have_o = false;
         if (n_tiles > 0 && fail == 0) {
-            if (__all_sync(0xffffffffu, mbar_wait(bar_o_full, 0, abort_flag))) { tc_fence_after_sync(); have_o = true; }
+            if (mbar_wait_warp(my_o_full, 0, abort_flag)) { tc_fence_after_sync(); have_o = true; }
             else fail = 9;
         }
         float inv = 0.0f;
         if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
         const bool row_ok = row < a.seqlen_q;
-        const float lse_val = (l_sum > 0.0f) ? (m_ref * 0.6931471805599453f + __logf(l_sum)) : -INFINITY;
+        const float lse_val = (l_sum > 0.0f) ? (m_ref * kLn2 + __logf(l_sum)) : -INFINITY;
         const long long unit_ll = unit;
         if (a.num_splits > 1) {
             const long long prow = (unit_ll * a.num_splits + split) * a.seqlen_q + row;
@@ -419,18 +628,18 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 5 && n_tiles > 0) {
+    if (warp == C::kMmaWarp && n_union > 0) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
 }
 
-template <int D, bool kBf16, bool kAlibi, bool kDropout>
+template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                        int units, cudaStream_t stream) {
-    auto kern = fwd_tiled_kernel<D, kBf16, kAlibi, kDropout>;
-    constexpr int smem = Cfg<D>::kSmemBytes;
+    auto kern = fwd_tiled_kernel<D, NQ, kBf16, kAlibi, kDropout>;
+    constexpr int smem = Cfg<D, NQ>::kSmemBytes;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -440,21 +649,29 @@ cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMa
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    const long long ctas = static_cast<long long>(units) * a.tr * a.num_splits;
+    const int trq = (a.tr + NQ - 1) / NQ;
+    const long long ctas = static_cast<long long>(units) * trq * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    kern<<<static_cast<unsigned>(ctas), kThreads, smem, stream>>>(tq, tk, tv, a);
+    kern<<<static_cast<unsigned>(ctas), Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, a);
     return cudaGetLastError();
 }
 
-template <int D, bool kBf16>
+template <int D, int NQ, bool kBf16>
 cudaError_t launch_flags(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                          int units, bool alibi, bool dropout, cudaStream_t stream) {
     if (alibi) {
-        return dropout ? launch_one<D, kBf16, true, true>(a, tq, tk, tv, units, stream)
-                       : launch_one<D, kBf16, true, false>(a, tq, tk, tv, units, stream);
+        return dropout ? launch_one<D, NQ, kBf16, true, true>(a, tq, tk, tv, units, stream)
+                       : launch_one<D, NQ, kBf16, true, false>(a, tq, tk, tv, units, stream);
     }
-    return dropout ? launch_one<D, kBf16, false, true>(a, tq, tk, tv, units, stream)
-                   : launch_one<D, kBf16, false, false>(a, tq, tk, tv, units, stream);
+    return dropout ? launch_one<D, NQ, kBf16, false, true>(a, tq, tk, tv, units, stream)
+                   : launch_one<D, NQ, kBf16, false, false>(a, tq, tk, tv, units, stream);
+}
+
+template <int D, int NQ>
+cudaError_t launch_dtype(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
+                         int units, bool bf16, bool alibi, bool dropout, cudaStream_t stream) {
+    return bf16 ? launch_flags<D, NQ, true>(a, tq, tk, tv, units, alibi, dropout, stream)
+                : launch_flags<D, NQ, false>(a, tq, tk, tv, units, alibi, dropout, stream);
 }
 
 }  // namespace
@@ -462,12 +679,15 @@ cudaError_t launch_flags(const FwdArgs& a, const CUtensorMap& tq, const CUtensor
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                              int units, bool bf16, bool dropout, cudaStream_t stream) {
     const bool alibi = a.alibi_slopes != nullptr;
+    // two query tiles per CTA once a unit has more than one; a single tile (decode-like
+    // shapes) keeps two independent CTAs per SM instead
+    const bool pair = a.tr >= 2;
     if (a.head_dim <= 64) {
-        return bf16 ? launch_flags<64, true>(a, tq, tk, tv, units, alibi, dropout, stream)
-                    : launch_flags<64, false>(a, tq, tk, tv, units, alibi, dropout, stream);
+        return pair ? launch_dtype<64, 2>(a, tq, tk, tv, units, bf16, alibi, dropout, stream)
+                    : launch_dtype<64, 1>(a, tq, tk, tv, units, bf16, alibi, dropout, stream);
     }
-    return bf16 ? launch_flags<128, true>(a, tq, tk, tv, units, alibi, dropout, stream)
-                : launch_flags<128, false>(a, tq, tk, tv, units, alibi, dropout, stream);
+    return pair ? launch_dtype<128, 2>(a, tq, tk, tv, units, bf16, alibi, dropout, stream)
+                : launch_dtype<128, 1>(a, tq, tk, tv, units, bf16, alibi, dropout, stream);
 }
 
 }  // namespace fa
