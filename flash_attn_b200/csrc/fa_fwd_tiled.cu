@@ -127,13 +127,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-// One lane polls, then every lane observes the completed phase itself.
+// Whole-warp wait: the lanes poll together (one shared-memory access per poll).  A poll is
+// slow while the tensor pipe streams operands from shared memory (several hundred cycles
+// were measured), so the wait is a single phase with no second look.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    int ok = 1;
-    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (ok) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
-    return __all_sync(0xffffffffu, ok) != 0;
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
 
 __device__ __forceinline__ bool elect_one() {
@@ -381,6 +379,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                                 issue_qk(i, st1);
                                 umma_commit(bar_s_full + 8 * i);
                                 FA_TR(24 + 10 * i);
+#if defined(FA_TRACE) && FA_TRACE == 2
+                                // development only: time the completion of this Q K^T on the issuing thread
+                                mbar_wait(bar_s_full + 8 * i, (tile + 1 - range[i].lo) & 1, abort_flag);
+                                FA_TR(25 + 10 * i);
+#endif
                             }
                         }
                         if (fail) break;
@@ -439,6 +442,13 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const int cb = t_lo + j;
             const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
             FA_TR(1);
+#if defined(FA_TRACE) && FA_TRACE == 2
+            {   // development only: count the polls lane 0 needs
+                int polls = 0;
+                if (lane == 0) { while (!mbar_test_wait(my_s_full, j & 1) && polls < 100000000) ++polls; }
+                FA_TR(100000 + polls);
+            }
+#endif
             if (!mbar_wait_warp(my_s_full, j & 1, abort_flag)) { fail = 8; break; }
             FA_TR(2);
             tc_fence_after_sync();

@@ -30,11 +30,15 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// Non-blocking phase test.  (mbarrier.try_wait may put the thread to sleep for a
+// hardware-chosen time slice; measured on B200 a sleeping waiter noticed a completed
+// phase up to ~1000 cycles late, which is most of a KV tile, so the waits spin on
+// test_wait instead.)
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -44,12 +48,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `abort_flag` is a CTA-wide shared int: once any thread gave up,
 // every other wait of the CTA returns false at its next poll.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
+        for (int i = 0; i < 256; ++i)
+            if (mbar_test_wait(bar, parity)) return true;
         if (*abort_flag != 0) return false;
         if (clock64() - t0 > kWaitCycles) {
             *abort_flag = 1;
