@@ -248,7 +248,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_init(bar_q_full, 1);
         for (int i = 0; i < NQ; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
-            mbar_init(bar_p_full + 8 * i, 128);
+            mbar_init(bar_p_full + 8 * i, 4);  // one arrival per softmax warp
             mbar_init(bar_o_full + 8 * i, 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
@@ -356,9 +356,15 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         const int st1 = (t + 1) % C::kStages;
                         const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
                         const bool more = t + 1 < n_union;
+                        // K/V tiles arrive long before they are needed; look at their barriers now,
+                        // while this thread would wait for P anyway, so that nothing sits between the
+                        // P V and Q K^T issues below (a poll is slow while MMAs stream from shared memory)
                         if (!mbar_wait(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
                         FA_TR(20);
-                        bool k_ready = false;
+                        if (more) {
+                            if (!mbar_wait(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
+                            FA_TR(23);
+                        }
 #pragma unroll
                         for (int i = 0; i < NQ; ++i) {
                             if (active(i, tile)) {
@@ -370,12 +376,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                                 FA_TR(22 + 10 * i);
                             }
                             if (more && active(i, tile + 1)) {
-                                if (!k_ready) {
-                                    if (!mbar_wait(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
-                                    FA_TR(23);
-                                    tc_fence_after_sync();
-                                    k_ready = true;
-                                }
+                                tc_fence_after_sync();
                                 issue_qk(i, st1);
                                 umma_commit(bar_s_full + 8 * i);
                                 FA_TR(24 + 10 * i);
@@ -565,7 +566,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(my_p_full);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(my_p_full);
             FA_TR(7);
             if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
         }
