@@ -123,6 +123,10 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->alibi_slopes = p->alibi_slopes;
     a->status = p->status;
     a->heads = p->heads;
+    a->units = p->batch * p->heads;
+    // query blocks of very different cost (causal, no left window): heaviest-first over groups of
+    // 16 units; otherwise unit-major, which keeps neighbouring CTAs on the same K/V tiles in L2
+    a->unit_group = (p->is_causal && p->window_left < 0) ? 16 : 1;
     a->seqlen_q = p->seqlen_q;
     a->seqlen_k = p->seqlen_k;
     a->head_dim = p->head_dim;

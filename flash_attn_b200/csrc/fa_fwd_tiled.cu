@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <type_traits>
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
 
@@ -50,6 +51,7 @@ namespace fa {
 namespace {
 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by > 2^8
+constexpr int kPolyPairsFrom = 3;  // of every 4 column pairs, pairs >= this use the polynomial exp2
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -119,6 +121,27 @@ __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// exp2 on the FMA/ALU pipes for a pair of arguments x <= ~8: the MUFU unit (16 results per
+// clock per SM) needs as long for the 128 x 128 exponentials of a tile pair as the tensor
+// pipe needs for their MMAs, so part of them is computed here instead.  Round to the nearest
+// integer n with the 1.5 * 2^23 trick, evaluate 2^f on f = x - n in [-0.5, 0.5] with a cubic
+// (max relative error 7.5e-5, far below the 16-bit rounding of P), and add n to the exponent.
+// Arguments below -126 give 2^-126 instead of 0.
+__device__ __forceinline__ float2 poly_exp2_pair(float2 x) {
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 magic = make_float2(12582912.0f, 12582912.0f);
+    const float2 r = __fadd2_rn(x, magic);
+    const float2 n = __fadd2_rn(r, make_float2(-12582912.0f, -12582912.0f));
+    const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
+    float2 p = __ffma2_rn(make_float2(0.0551716685f, 0.0551716685f), f, make_float2(0.2426111251f, 0.2426111251f));
+    p = __ffma2_rn(p, f, make_float2(0.6932609677f, 0.6932609677f));
+    p = __ffma2_rn(p, f, make_float2(0.9999280572f, 0.9999280572f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
+    return p;
 }
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -225,8 +248,15 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // ---- which query tiles does this CTA own ------------------------------------
     const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
     const int per_unit = trq * a.num_splits;
-    const int unit = blockIdx.x / per_unit;
-    const int bx = blockIdx.x - unit * per_unit;
+    // CTA order: groups of unit_group units; inside a group all units' first query block, then
+    // all second ones, ...  With a causal mask the blocks are visited heaviest first, so the
+    // grid is close to a longest-job-first schedule while the K/V working set of the CTAs in
+    // flight (one group) stays far below the L2 size.
+    const int unit0 = (blockIdx.x / (a.unit_group * per_unit)) * a.unit_group;
+    const int gsize = min(a.unit_group, a.units - unit0);
+    const int rem = blockIdx.x - unit0 * per_unit;
+    const int unit = unit0 + rem % gsize;
+    const int bx = rem / gsize;
     const int split = bx % a.num_splits;
     int qb = bx / a.num_splits;
     if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
@@ -470,7 +500,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
             if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
             if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
-            if (__any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1)) {
+            const bool tile_masked = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
+            if (tile_masked) {
 #pragma unroll
                 for (int c = 0; c < 128; ++c)
                     if (c < c_lo || c > c_hi) s[c] = -INFINITY;
@@ -537,31 +568,42 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
             const float2 neg_m2 = make_float2(neg_m, neg_m);
             const float2 scale22 = make_float2(scale2, scale2);
+            // On tiles without masked elements (every score finite, so no argument is -inf) pairs
+            // kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.
+            auto exp_tile = [&](auto poly_tag) {
+                constexpr int kPolyFrom = decltype(poly_tag)::value;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t pr[32];
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t pr[32];
 #pragma unroll
-                for (int g = 0; g < 8; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
-                    uint32_t msk = 0xffffffffu;
-                    if constexpr (kDropout) {
-                        const uint32_t two = (keep_bits >> (2 * (c * 8 + g))) & 3u;
-                        msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
+                    for (int g = 0; g < 8; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
+                        uint32_t msk = 0xffffffffu;
+                        if constexpr (kDropout) {
+                            const uint32_t two = (keep_bits >> (2 * (c * 8 + g))) & 3u;
+                            msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int col = c * 64 + g * 8 + q * 2;
+                            float2 x = make_float2(s[col], s[col + 1]);
+                            if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
+                            else x = __ffma2_rn(x, scale22, neg_m2);
+                            float2 p;
+                            if (q >= kPolyFrom) {
+                                p = poly_exp2_pair(x);
+                            } else {
+                                p.x = fast_exp2(x.x);
+                                p.y = fast_exp2(x.y);
+                            }
+                            acc[q] = __fadd2_rn(acc[q], p);
+                            pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
+                        }
                     }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int col = c * 64 + g * 8 + q * 2;
-                        float2 x = make_float2(s[col], s[col + 1]);
-                        if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
-                        else x = __ffma2_rn(x, scale22, neg_m2);
-                        float2 p;
-                        p.x = fast_exp2(x.x);
-                        p.y = fast_exp2(x.y);
-                        acc[q] = __fadd2_rn(acc[q], p);
-                        pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
-                    }
+                    tmem_st32(tmem_p + lane_base + c * 32, pr);
                 }
-                tmem_st32(tmem_p + lane_base + c * 32, pr);
-            }
+            };
+            if (tile_masked) exp_tile(std::integral_constant<int, 4>{});
+            else exp_tile(std::integral_constant<int, kPolyPairsFrom>{});
             FA_TR(6);
             l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();

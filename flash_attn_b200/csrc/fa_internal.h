@@ -19,6 +19,8 @@ struct FwdArgs {
     const float* alibi_slopes;
     int* status;
     int heads;
+    int units;              // batch * heads of this launch
+    int unit_group;         // units whose CTAs are interleaved in launch order (1 = unit-major)
     int seqlen_q, seqlen_k, head_dim;
     int tr, tc;             // query / key tiles
     int num_splits, tiles_per_split;
