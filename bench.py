@@ -36,6 +36,9 @@ WORKLOADS = {
                desc="config 2: bf16 [8,16,2048,128] causal, dropout 0.1 (Philox seed 42, offset 0)"),
     "c3": dict(B=4, H=32, Nq=8192, Nk=8192, d=128, causal=True, window=(1024, 0), alibi=True, p=0.0, splits=1,
                desc="config 3: bf16 [4,32,8192,128] causal + window(1024,0) + ALiBi 2^(-8(h+1)/32)"),
+    "c5": dict(B=1, H=32, Nq=131072, Nk=131072, d=128, causal=True, window=(-1, -1), alibi=False, p=0.0, splits=1,
+               desc="config 5: bf16 [1,32,131072,128] causal, N(0,0.5), sequence ring over the ranks (zig-zag chunks, "
+                    "NCCL send/recv, LSE merge)"),
     "c4": dict(B=64, H=32, Nq=1, Nk=32768, d=128, causal=False, window=(-1, -1), alibi=False, p=0.0, splits=16,
                desc="config 4: split-KV decode bf16 B=64 H=32 q=1 kv=32768 d=128, 16 splits + LSE combine"),
 }
@@ -61,7 +64,7 @@ def attended_pairs(w):
 def work_per_step(name, w):
     """(flops, bytes) of one step on one GPU, by the conventions stated in DESIGN.md."""
     units = w["B"] * w["H"]
-    if name == "c2":
+    if name in ("c2", "c5"):
         flops = 4.0 * units * w["Nq"] * w["Nk"] * w["d"] / 2  # causal convention 4*B*H*N^2*d/2
     else:
         flops = 4.0 * units * attended_pairs(w) * w["d"]
@@ -305,6 +308,62 @@ def time_e2e(torch, fa, w, steps, warmup, rank):
     return dt, h2d, d2h
 
 
+def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks):
+    """Config 5: ONE problem sharded over the ranks (strong scaling): each rank holds two zig-zag
+    chunks of the sequence; K/V chunks go round the ring while the forward kernel works."""
+    from flash_attn_b200 import ring
+    N, C = w["Nq"], w["Nq"] // (2 * world)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5 + rank)
+    mk = lambda: [(0.5 * torch.randn((w["B"], w["H"], C, w["d"]), generator=g, device=dev)).bfloat16() for _ in range(2)]
+    q, k, v = mk(), mk(), mk()
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        sampler.wait_first_sample()
+    for _ in range(args.warmup):
+        ring.ring_attention_forward(q, k, v, causal=True)
+    barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ring.ring_attention_forward(q, k, v, causal=True)
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    sec = max_over_ranks(e0.elapsed_time(e1) / 1e3 / args.steps)
+    clocks = sampler.stop() if sampler else None
+    value = flops / sec / 1e12
+    # kernel launches per step and rank: one forward + one merge per visited (query chunk, key chunk) pair, two casts
+    pairs = sum(1 for s in range(world) for a in ring.zigzag_chunks(rank, world)
+                for b in ring.zigzag_chunks((rank - s) % world, world) if b <= a)
+    line = {
+        "metric": "fwd_attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["desc"], "chunk_rows": C, "kv_bytes_per_ring_step_per_rank": 4 * w["B"] * w["H"] * C * w["d"] * 2,
+                   "l2": "each rank streams 2 x %d MB of K/V per ring step (> L2)" % (2 * w["H"] * C * w["d"] * 2 // 2 ** 20),
+                   "flops_per_step_total": flops},
+        "clocks": clocks,
+        "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "the ring works on device-resident shards; the host-buffer path is measured on config 2"},
+        "gpu_launches": (2 * pairs + 2) * args.steps * world,
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tensor_sustained"] or peaks["tensor"],
+                     "unit": "TFLOP/s", "frac": value / world / (peaks["tensor_sustained"] or peaks["tensor"]),
+                     "peak_source": peaks["source"] + " sustained (seconds-long step)", "traffic": None,
+                     "kernel": "fwd_tiled_kernel"},
+    }
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -353,6 +412,8 @@ def main():
     w = WORKLOADS[name]
     flops, nbytes = work_per_step(name, w)
     peaks = load_peaks()
+    if name == "c5":
+        return run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks)
     # two input sets (2 x 268 MB for config 2) alternate, so no step finds its inputs in the 126 MB L2
     sets = make_inputs(torch, w, 2 + rank, dev, copies=2 if name != "c4" else 1)
 
