@@ -367,7 +367,7 @@ def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=None, help="default: 2000 (c2), 200 (c3), 50 (c4), 5 (c5)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
@@ -375,6 +375,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"c2": 2000, "c3": 200, "c4": 50, "c5": 5}[args.workload] if args.impl == "ours" else 2
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
