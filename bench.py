@@ -389,6 +389,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"  # keeps NCCL's version banner off stdout: rank 0 prints one JSON line
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
@@ -485,6 +487,21 @@ def main():
             except Exception as exc:  # a side measurement must not lose the main line
                 side[other] = {"error": repr(exc)}
         line["secondary"] = side
+
+    if rank == 0 and world == 1 and not args.no_secondary and name == "c2":
+        # the reference's own kernels (fp16, recompiled for sm_100a) on the same shape, for context
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import ref_gpu
+            if ref_gpu.available():
+                qh, kh, vh = (torch.randn((w["B"], w["H"], w["Nq"], w["d"]), device=dev).half() for _ in range(3))
+                _, used, us = ref_gpu.forward(qh, kh, vh, w["d"] ** -0.5, causal=True, iters=5)
+                line["reference_gpu_kernels"] = {"what": "reference forward_kernel (mma.sync, fp16, causal, no dropout, "
+                                                 "fp32 O) recompiled for sm_100a", "ms": us / 1e3,
+                                                 "tflops": flops / (us * 1e-6) / 1e12, "splits": used}
+                del qh, kh, vh
+        except Exception as exc:
+            line["reference_gpu_kernels"] = {"error": repr(exc)}
 
     if rank == 0 and world == 1 and not args.no_cpu:
         try:

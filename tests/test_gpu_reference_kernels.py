@@ -1,0 +1,64 @@
+"""Parity with the reference's own CUDA kernels, run on the same GPU.
+
+The dropout mask is read out of the reference's forward_kernel itself (unmodified,
+recompiled for sm_100a): with Q = K = 0 every probability is 1/N, and with V a
+tile-weighted identity the fp32 output encodes which entries were kept.  This pins
+the stateless Philox map against the real thing, not only against the host
+simulation.  Skipped when oracle/_ref/libref_gpu.so was not built."""
+import numpy as np
+import pytest
+import torch
+
+import gpu_util
+import oracle_lib
+import ref_gpu
+import synth
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_gpu.available(), reason="reference kernels not built")]
+
+
+def _reference_mask(B, H, N, p, seed, split_num=1):
+    d, tiles = 128, (N + 127) // 128
+    q = torch.zeros(B, H, N, d, dtype=torch.float16, device="cuda")
+    v = torch.zeros(B, H, N, d, dtype=torch.float32, device="cuda")
+    idx = torch.arange(N, device="cuda")
+    v[:, :, idx, idx % 128] = (2.0 ** (idx // 128)).float()
+    o, used, _ = ref_gpu.forward(q, q, v.half(), 1.0, p_dropout=p, seed=seed, split_num=split_num)
+    code = torch.round(o * (N * (1.0 - np.float32(p).item()))).to(torch.int64)
+    keep = torch.zeros(B, H, N, tiles * 128, dtype=torch.uint8, device="cuda")
+    for t in range(tiles):
+        keep[..., t * 128:(t + 1) * 128] = ((code >> t) & 1).to(torch.uint8)
+    return keep[..., :N].cpu().numpy(), used
+
+
+@pytest.mark.parametrize("case", [dict(B=1, H=2, N=256, p=0.1, seed=42), dict(B=2, H=1, N=512, p=0.25, seed=48),
+                                  dict(B=1, H=2, N=512, p=0.1, seed=7, split_num=2)])
+def test_reference_kernel_mask_equals_the_stateless_map(case):
+    import flash_attn_b200 as fa
+    splits = case.get("split_num", 1)
+    got_ref, used = _reference_mask(case["B"], case["H"], case["N"], case["p"], case["seed"], splits)
+    assert used == splits
+    want = oracle_lib.dropout_mask(case["B"], case["H"], case["N"], case["N"], np.float32(case["p"]).item(),
+                                   case["seed"], 0, splits)
+    assert np.array_equal(got_ref, want)
+    ours = fa.dropout_mask(case["B"], case["H"], case["N"], case["N"], case["p"], case["seed"], 0, splits).cpu().numpy()
+    assert np.array_equal(ours, got_ref)
+
+
+@pytest.mark.parametrize("case", [
+    dict(B=1, H=4, N=256, d=64, causal=False),
+    dict(B=2, H=2, N=512, d=128, causal=True),
+    dict(B=1, H=2, N=384, d=128, causal=False, window=(128, 128)),
+    dict(B=1, H=4, N=256, d=64, causal=False, split_num=2),
+])
+def test_outputs_match_the_reference_kernels(case):
+    import flash_attn_b200 as fa
+    B, H, N, d = case["B"], case["H"], case["N"], case["d"]
+    q, k, v = (gpu_util.to_dev(x, "float16") for x in synth.qkv(40, B, H, N, N, d, "float16"))
+    window = case.get("window", (-1, -1))
+    o_ref, _, _ = ref_gpu.forward(q, k, v, d ** -0.5, causal=case["causal"], window=window,
+                                  split_num=case.get("split_num", 1))
+    o, _ = fa.flash_attn_forward(q, k, v, causal=case["causal"], window=window, out_dtype=torch.float32,
+                                 num_splits=case.get("split_num", 1))
+    err = (o - o_ref).abs()
+    assert err.max().item() <= gpu_util.O_MAX_ABS and err.mean().item() <= gpu_util.O_MEAN_ABS, (err.max(), err.mean())
