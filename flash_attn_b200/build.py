@@ -12,7 +12,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libfa_b200.so")
-SOURCES = ["fa_api.cu", "fa_fwd_tiled.cu", "fa_aux.cu", "fa_static_scratch.cu"]
+SOURCES = ["fa_api.cu", "fa_fwd_tiled.cu", "fa_decode.cu", "fa_aux.cu", "fa_static_scratch.cu"]
 HEADERS = ["fa_internal.h", "sm100_ptx.cuh", "philox.cuh", os.path.join("..", "..", "include", "fa_b200.h")]
 
 

@@ -3,6 +3,7 @@
 // of the reference's main() (src/main.cu:109-205) with every compile-time switch
 // (src/main.cu:39-49) turned into a run-time parameter.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -149,6 +150,15 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->drop.inv_keep = p->p_dropout > 0.0f ? 1.0f / (1.0f - p->p_dropout) : 1.0f;
 }
 
+// Development switch: FA_B200_DECODE=0 sends seqlen_q = 1 launches through the tiled kernel.
+bool decode_kernel_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("FA_B200_DECODE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 size_t partial_bytes(const fa_fwd_params* p, int splits, size_t* lse_off) {
     const size_t rows = static_cast<size_t>(p->batch) * p->heads * splits * p->seqlen_q;
     const size_t o_bytes = (rows * p->head_dim * sizeof(float) + 255) & ~static_cast<size_t>(255);
@@ -237,7 +247,21 @@ int fa_fwd(const fa_fwd_params* p) {
     if ((rc = make_tensor_map(&tq, bf16, p->q, p->head_dim, p->seqlen_q, units)) != FA_OK) return rc;
     if ((rc = make_tensor_map(&tk, bf16, p->k, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
     if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
-    if (launch_fwd_tiled(a, tq, tk, tv, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) return FA_ERR_CUDA;
+    if (p->seqlen_q == 1 && decode_kernel_enabled()) {
+        // one query row per unit: the streaming kernel with keys on the tensor-memory lanes
+        DecodeArgs d;
+        std::memset(&d, 0, sizeof(d));
+        d.q = p->q; d.o = p->o; d.lse = p->lse;
+        d.o_partial = a.o_partial; d.lse_partial = a.lse_partial;
+        d.alibi_slopes = p->alibi_slopes; d.status = p->status;
+        d.heads = p->heads; d.seqlen_k = p->seqlen_k; d.head_dim = p->head_dim; d.tc = a.tc;
+        d.num_splits = splits; d.tiles_per_split = a.tiles_per_split; d.scale_log2 = a.scale_log2;
+        d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
+        d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;
+        if (launch_decode(d, tk, tv, units, bf16, stream) != cudaSuccess) return FA_ERR_CUDA;
+    } else if (launch_fwd_tiled(a, tq, tk, tv, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) {
+        return FA_ERR_CUDA;
+    }
     if (splits > 1) {
         CombineArgs c;
         c.o_partial = a.o_partial;

@@ -35,6 +35,28 @@ struct FwdArgs {
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                              int units, bool bf16, bool dropout, cudaStream_t stream);
 
+// Device-side argument block of the decode kernel (seqlen_q = 1).
+struct DecodeArgs {
+    const void* q;          // [units, d]
+    void* o;                // [units, d] (non-split)
+    float* lse;             // [units] or null
+    float* o_partial;       // [units, splits, d] fp32 (split)
+    float* lse_partial;     // [units, splits]
+    const float* alibi_slopes;
+    int* status;
+    int heads;
+    int seqlen_k, head_dim;
+    int tc;
+    int num_splits, tiles_per_split;
+    float scale_log2;
+    int is_causal, window_left, window_right;
+    long long q_pos0, k_pos0;
+    int o_is_fp32;
+    DropoutParams drop;
+};
+cudaError_t launch_decode(const DecodeArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int units, bool bf16,
+                          cudaStream_t stream);
+
 struct CombineArgs {
     const float* o_partial; const float* lse_partial;
     void* o; float* lse;
