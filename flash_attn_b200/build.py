@@ -54,6 +54,25 @@ def build(force=False, verbose=False):
     return LIB
 
 
+BENCH = os.path.join(PKG, "fa_bench")
+
+
+def build_driver(force=False):
+    """Builds the C benchmark driver (csrc/fa_main.c) against the library with gcc."""
+    src = os.path.join(CSRC, "fa_main.c")
+    build()
+    if not force and os.path.exists(BENCH) and os.path.getmtime(BENCH) > max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        return BENCH
+    cuda = os.path.dirname(os.path.dirname(nvcc_path()))
+    cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
+    subprocess.check_call([cc, "-std=c99", "-O2", "-Wall", "-I", os.path.join(PKG, "..", "include"),
+                           "-I", os.path.join(cuda, "include"), src, "-o", BENCH,
+                           "-L", PKG, "-lfa_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm",
+                           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")])
+    return BENCH
+
+
 if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(LIB)
+    print(build_driver(force="--force" in sys.argv))
