@@ -25,12 +25,12 @@ def _run(args):
         return json.loads(out.strip().splitlines()[-1]), open(dump, "rb").read()
 
 
-def _check(raw, units, Nq, Nk, d, dtype, seed, **kw):
+def _check(raw, units, Nq, Nk, d, dtype, data_seed, **kw):
     n = units * Nq * d
     tdt = gpu_util.TORCH_DT[dtype]
     o = torch.frombuffer(bytearray(raw[:2 * n]), dtype=tdt).float().numpy().reshape(1, units, Nq, d)
     lse = np.frombuffer(raw[2 * n:2 * n + 4 * units * Nq], dtype=np.float32).reshape(1, units, Nq)
-    q, k, v = synth.qkv(seed, 1, units, Nq, Nk, d, dtype)
+    q, k, v = synth.qkv(data_seed, 1, units, Nq, Nk, d, dtype)
     want_o, want_lse = oracle_lib.forward(q, k, v, 1 / np.sqrt(d), **kw)
     err = np.abs(o - want_o)
     assert err.max() <= gpu_util.O_MAX_ABS and err.mean() <= gpu_util.O_MEAN_ABS, (err.max(), err.mean())
