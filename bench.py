@@ -374,6 +374,8 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the c3/c4 side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
+    ap.add_argument("--batch", type=int, default=None, help="override the workload's batch size (smaller cases "
+                    "for profiler captures; the JSON line then describes the reduced workload)")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"c2": 2000, "c3": 200, "c4": 50, "c5": 5}[args.workload] if args.impl == "ours" else 2
@@ -413,7 +415,10 @@ def main():
         return float(t.item())
 
     name = args.workload
-    w = WORKLOADS[name]
+    w = dict(WORKLOADS[name])
+    if args.batch is not None:
+        w["B"] = args.batch
+        w["desc"] += f" [batch reduced to {args.batch}]"
     flops, nbytes = work_per_step(name, w)
     peaks = load_peaks()
     if name == "c5":
@@ -451,7 +456,7 @@ def main():
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof["peak_source"] = peaks["source"] + (" burst" if not is_decode else " copy")
     roof["traffic"] = None  # DRAM bytes per launch from ncu: see profiles/
-    roof["kernel"] = "fwd_tiled_kernel"
+    roof["kernel"] = "decode_kernel (+ combine_kernel)" if is_decode else "fwd_tiled_kernel"
     launches_per_step = 1 if w["splits"] <= 1 else 2
 
     line = {
