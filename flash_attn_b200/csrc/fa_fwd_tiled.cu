@@ -74,7 +74,7 @@ struct Cfg {
     static constexpr int kSmemK = NQ * kTileBytes;
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
     static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-    static constexpr int kNumBars = 1 + 3 * NQ + 4 * kStages;
+    static constexpr int kNumBars = 1 + 4 * NQ + 4 * kStages;
     static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
 };
 
@@ -202,16 +202,25 @@ __device__ __forceinline__ void issue_qk_block(uint32_t d_tmem, uint32_t qa_lo, 
 #define FA_PV_STEP                                                                             \
     "add.u32 pa, pa, 8;\n\tadd.u32 vb, vb, 128;\n\tmov.b64 db, {vb, %3};\n\t"                    \
     "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p1;\n\t"
-__device__ __forceinline__ void issue_pv_block(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
+#define FA_PV_HEAD                                                                             \
+    "{\n\t.reg .pred p0, p1;\n\t.reg .b32 pa, vb;\n\t.reg .b64 db;\n\t"                          \
+    "setp.ne.b32 p0, %5, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"                                        \
+    "mov.b32 pa, %1;\n\tmov.b32 vb, %2;\n\tmov.b64 db, {vb, %3};\n\t"                            \
+    "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p0;\n\t"
+// k-steps [0, kSplitSteps) of a tile: issued as soon as the first kSplitSteps*16 columns of P
+// are in tensor memory; the rest follow when P is complete.
+constexpr int kSplitSteps = 6;
+__device__ __forceinline__ void issue_pv_first(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
                                                uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p0, p1;\n\t.reg .b32 pa, vb;\n\t.reg .b64 db;\n\t"
-        "setp.ne.b32 p0, %5, 0;\n\tsetp.eq.b32 p1, 0, 0;\n\t"
-        "mov.b32 pa, %1;\n\tmov.b32 vb, %2;\n\tmov.b64 db, {vb, %3};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p0;\n\t"
-        FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
-        ::"r"(d_tmem), "r"(a_tmem), "r"(vb_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
-        : "memory");
+    asm volatile(FA_PV_HEAD FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
+                 ::"r"(d_tmem), "r"(a_tmem), "r"(vb_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+__device__ __forceinline__ void issue_pv_rest(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
+                                              uint32_t idesc) {
+    asm volatile(FA_PV_HEAD FA_PV_STEP "}"
+                 ::"r"(d_tmem), "r"(a_tmem + kSplitSteps * 8), "r"(vb_lo + kSplitSteps * 128), "r"(desc_hi), "r"(idesc), "r"(1u)
+                 : "memory");
 }
 
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
@@ -231,7 +240,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t bar_q_full = bar0;
     const uint32_t bar_s_full = bar0 + 8;                        // [NQ]
     const uint32_t bar_p_full = bar_s_full + 8 * NQ;             // [NQ]
-    const uint32_t bar_o_full = bar_p_full + 8 * NQ;             // [NQ]
+    const uint32_t bar_p_part = bar_p_full + 8 * NQ;             // [NQ] first kSplitSteps*16 columns of P
+    const uint32_t bar_o_full = bar_p_part + 8 * NQ;             // [NQ]
     const uint32_t bar_k_full = bar_o_full + 8 * NQ;             // [kStages]
     const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;    // [kStages]
@@ -279,6 +289,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int i = 0; i < NQ; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
             mbar_init(bar_p_full + 8 * i, 4);  // one arrival per softmax warp
+            mbar_init(bar_p_part + 8 * i, 4);
             mbar_init(bar_o_full + 8 * i, 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
@@ -362,9 +373,13 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
                                       k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
                 };
-                auto issue_pv = [&](int i, int st, uint32_t accumulate) {
-                    issue_pv_block(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
+                auto issue_pv_a = [&](int i, int st, uint32_t accumulate) {
+                    issue_pv_first(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
                                    v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv, accumulate);
+                };
+                auto issue_pv_b = [&](int i, int st) {
+                    issue_pv_rest(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
+                                  v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv);
                 };
                 auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
                 do {
@@ -398,10 +413,14 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
                         for (int i = 0; i < NQ; ++i) {
                             if (active(i, tile)) {
-                                if (!mbar_wait(bar_p_full + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
+                                // P V starts on the first three quarters of P while the last is exponentiated
+                                if (!mbar_wait(bar_p_part + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
                                 FA_TR(21 + 10 * i);
                                 tc_fence_after_sync();
-                                issue_pv(i, st, tile > range[i].lo ? 1u : 0u);
+                                issue_pv_a(i, st, tile > range[i].lo ? 1u : 0u);
+                                if (!mbar_wait(bar_p_full + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
+                                tc_fence_after_sync();
+                                issue_pv_b(i, st);
                                 if (tile == range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
                                 FA_TR(22 + 10 * i);
                             }
@@ -441,6 +460,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t tmem_o = tmem_base + C::kTmemO + qi * D;  // O accumulator, D fp32 columns
         const uint32_t my_s_full = bar_s_full + 8 * qi;
         const uint32_t my_p_full = bar_p_full + 8 * qi;
+        const uint32_t my_p_part = bar_p_part + 8 * qi;
         const uint32_t my_o_full = bar_o_full + 8 * qi;
         float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
         float l_sum = 0.0f;
@@ -472,6 +492,12 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         for (int j = 0; j < n_tiles; ++j) {
             const int cb = t_lo + j;
             const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
+            // columns this row may attend to inside the tile: [c_lo, c_hi] (worked out before S arrives)
+            int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
+            if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
+            if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
+            if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
+            const bool tile_masked_pre = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
             FA_TR(1);
 #if defined(FA_TRACE) && FA_TRACE == 2
             {   // development only: count the polls lane 0 needs
@@ -495,12 +521,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             FA_TR(3);
 
-            // columns this row may attend to inside the tile: [c_lo, c_hi]
-            int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
-            if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
-            if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
-            if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
-            const bool tile_masked = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
+            const bool tile_masked = tile_masked_pre;
             if (tile_masked) {
 #pragma unroll
                 for (int c = 0; c < 128; ++c)
@@ -573,18 +594,18 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             auto exp_tile = [&](auto poly_tag) {
                 constexpr int kPolyFrom = decltype(poly_tag)::value;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t pr[32];
+                for (int c = 0; c < 4; ++c) {  // quarters of 32 columns
+                    uint32_t pr[16];
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
+                    for (int g = 0; g < 4; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
                         uint32_t msk = 0xffffffffu;
                         if constexpr (kDropout) {
-                            const uint32_t two = (keep_bits >> (2 * (c * 8 + g))) & 3u;
+                            const uint32_t two = (keep_bits >> (2 * (c * 4 + g))) & 3u;
                             msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
                         }
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            const int col = c * 64 + g * 8 + q * 2;
+                            const int col = c * 32 + g * 8 + q * 2;
                             float2 x = make_float2(s[col], s[col + 1]);
                             if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
                             else x = __ffma2_rn(x, scale22, neg_m2);
@@ -599,7 +620,14 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
                         }
                     }
-                    tmem_st32(tmem_p + lane_base + c * 32, pr);
+                    tmem_st16(tmem_p + lane_base + c * 16, pr);
+                    if (c == (kSplitSteps * 16) / 32 - 1) {
+                        // the first kSplitSteps*16 columns are stored: let the MMA warp start P V on them
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(my_p_part);
+                    }
                 }
             };
             if (tile_masked) exp_tile(std::integral_constant<int, 4>{});
