@@ -74,7 +74,7 @@ struct Cfg {
     static constexpr int kSmemK = NQ * kTileBytes;
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
     static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-    static constexpr int kNumBars = 1 + 4 * NQ + 4 * kStages;
+    static constexpr int kNumBars = 1 + 2 * NQ + 4 * kStages;
     static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
 };
 
@@ -155,6 +155,19 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // were measured), so the wait is a single phase with no second look.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
+}
+
+// Hardware named barriers carry the P hand-over: the 128 threads of a softmax warpgroup
+// arrive (non-blocking), the MMA warp syncs.  Waking from a named barrier costs tens of
+// cycles, while a poll of a shared-memory mbarrier took several hundred whenever the tensor
+// pipe was streaming operands.  A named barrier cannot time out, so a softmax thread that
+// leaves its loop early still posts every arrival it owes (see the end of its loop).
+constexpr int kPBarrierThreads = 160;  // 128 softmax threads + the MMA warp
+__device__ __forceinline__ void named_arrive(int id) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kPBarrierThreads) : "memory");
+}
+__device__ __forceinline__ void named_sync(int id) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kPBarrierThreads) : "memory");
 }
 
 __device__ __forceinline__ bool elect_one() {
@@ -239,9 +252,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // barrier map
     const uint32_t bar_q_full = bar0;
     const uint32_t bar_s_full = bar0 + 8;                        // [NQ]
-    const uint32_t bar_p_full = bar_s_full + 8 * NQ;             // [NQ]
-    const uint32_t bar_p_part = bar_p_full + 8 * NQ;             // [NQ] first kSplitSteps*16 columns of P
-    const uint32_t bar_o_full = bar_p_part + 8 * NQ;             // [NQ]
+    const uint32_t bar_o_full = bar_s_full + 8 * NQ;             // [NQ]
     const uint32_t bar_k_full = bar_o_full + 8 * NQ;             // [kStages]
     const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;    // [kStages]
@@ -288,8 +299,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         mbar_init(bar_q_full, 1);
         for (int i = 0; i < NQ; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
-            mbar_init(bar_p_full + 8 * i, 4);  // one arrival per softmax warp
-            mbar_init(bar_p_part + 8 * i, 4);
             mbar_init(bar_o_full + 8 * i, 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
@@ -358,34 +367,37 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
         } else if (n_union > 0 && warp == C::kMmaWarp) {
             // ======================= MMA issuer =====================================
-            if (elect_one()) {
-                constexpr uint32_t idesc_qk = make_idesc_f16(kTile, kTile, kBf16, false);
-                constexpr uint32_t idesc_pv = make_idesc_f16(kTile, D, kBf16, true);
-                // Descriptor words.  High word: SBO = 1024, 128-byte swizzle, version 1; low word:
-                // start address (and for V the LBO of 16 KB between its two 64-column halves).
-                const uint64_t dqk = make_smem_desc(0, 0, 1024);
-                const uint64_t dvv = make_smem_desc(0, kTile * 128, 1024);
-                const uint32_t desc_hi = static_cast<uint32_t>(dqk >> 32);
-                const uint32_t q_lo = static_cast<uint32_t>(dqk) | (sQ >> 4);
-                const uint32_t k_lo = static_cast<uint32_t>(dqk) | (sK >> 4);
-                const uint32_t v_lo = static_cast<uint32_t>(dvv) | (sV >> 4);
-                auto issue_qk = [&](int i, int st) {
-                    issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
-                                      k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
-                };
-                auto issue_pv_a = [&](int i, int st, uint32_t accumulate) {
-                    issue_pv_first(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
-                                   v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv, accumulate);
-                };
-                auto issue_pv_b = [&](int i, int st) {
-                    issue_pv_rest(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
-                                  v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv);
-                };
-                auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
-                do {
-                    if (!mbar_wait(bar_q_full, 0, abort_flag)) { fail = 3; break; }
-                    if (!mbar_wait(bar_k_full, 0, abort_flag)) { fail = 4; break; }
-                    tc_fence_after_sync();
+            // The warp walks the loop together (it meets the softmax warpgroups at named
+            // barriers); one elected lane issues the MMAs and commits.
+            const bool leader = elect_one();
+            constexpr uint32_t idesc_qk = make_idesc_f16(kTile, kTile, kBf16, false);
+            constexpr uint32_t idesc_pv = make_idesc_f16(kTile, D, kBf16, true);
+            // Descriptor words.  High word: SBO = 1024, 128-byte swizzle, version 1; low word:
+            // start address (and for V the LBO of 16 KB between its two 64-column halves).
+            const uint64_t dqk = make_smem_desc(0, 0, 1024);
+            const uint64_t dvv = make_smem_desc(0, kTile * 128, 1024);
+            const uint32_t desc_hi = static_cast<uint32_t>(dqk >> 32);
+            const uint32_t q_lo = static_cast<uint32_t>(dqk) | (sQ >> 4);
+            const uint32_t k_lo = static_cast<uint32_t>(dqk) | (sK >> 4);
+            const uint32_t v_lo = static_cast<uint32_t>(dvv) | (sV >> 4);
+            auto issue_qk = [&](int i, int st) {
+                issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
+                                  k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
+            };
+            auto issue_pv_a = [&](int i, int st, uint32_t accumulate) {
+                issue_pv_first(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
+                               v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv, accumulate);
+            };
+            auto issue_pv_b = [&](int i, int st) {
+                issue_pv_rest(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
+                              v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv);
+            };
+            auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
+            do {
+                if (!mbar_wait_warp(bar_q_full, 0, abort_flag)) { fail = 3; break; }
+                if (!mbar_wait_warp(bar_k_full, 0, abort_flag)) { fail = 4; break; }
+                tc_fence_after_sync();
+                if (leader) {
 #pragma unroll
                     for (int i = 0; i < NQ; ++i) {
                         if (active(i, lo)) {
@@ -394,54 +406,52 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         }
                     }
                     umma_commit(bar_k_empty);
-                    for (int t = 0; t < n_union && fail == 0; ++t) {
-                        const int tile = lo + t;
-                        const int st = t % C::kStages;
-                        const uint32_t ph = (t / C::kStages) & 1;
-                        const int st1 = (t + 1) % C::kStages;
-                        const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
-                        const bool more = t + 1 < n_union;
-                        // K/V tiles arrive long before they are needed; look at their barriers now,
-                        // while this thread would wait for P anyway, so that nothing sits between the
-                        // P V and Q K^T issues below (a poll is slow while MMAs stream from shared memory)
-                        if (!mbar_wait(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
-                        FA_TR(20);
-                        if (more) {
-                            if (!mbar_wait(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
-                            FA_TR(23);
-                        }
+                }
+                for (int t = 0; t < n_union && fail == 0; ++t) {
+                    const int tile = lo + t;
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int st1 = (t + 1) % C::kStages;
+                    const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
+                    const bool more = t + 1 < n_union;
+                    // K/V tiles arrive long before they are needed; their barriers are looked at now,
+                    // while the warp would wait for P anyway
+                    if (!mbar_wait_warp(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
+                    FA_TR(20);
+                    if (more) {
+                        if (!mbar_wait_warp(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
+                        FA_TR(23);
+                    }
 #pragma unroll
-                        for (int i = 0; i < NQ; ++i) {
-                            if (active(i, tile)) {
-                                // P V starts on the first three quarters of P while the last is exponentiated
-                                if (!mbar_wait(bar_p_part + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
-                                FA_TR(21 + 10 * i);
-                                tc_fence_after_sync();
-                                issue_pv_a(i, st, tile > range[i].lo ? 1u : 0u);
-                                if (!mbar_wait(bar_p_full + 8 * i, (tile - range[i].lo) & 1, abort_flag)) { fail = 5; break; }
-                                tc_fence_after_sync();
+                    for (int i = 0; i < NQ; ++i) {
+                        if (active(i, tile)) {
+                            // P V starts on the first three quarters of P while the last is exponentiated
+                            named_sync(1 + 2 * i);
+                            FA_TR(21 + 10 * i);
+                            tc_fence_after_sync();
+                            if (leader) issue_pv_a(i, st, tile > range[i].lo ? 1u : 0u);
+                            named_sync(2 + 2 * i);
+                            tc_fence_after_sync();
+                            if (leader) {
                                 issue_pv_b(i, st);
                                 if (tile == range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
-                                FA_TR(22 + 10 * i);
                             }
-                            if (more && active(i, tile + 1)) {
-                                tc_fence_after_sync();
+                            FA_TR(22 + 10 * i);
+                        }
+                        if (more && active(i, tile + 1)) {
+                            if (leader) {
                                 issue_qk(i, st1);
                                 umma_commit(bar_s_full + 8 * i);
-                                FA_TR(24 + 10 * i);
-#if defined(FA_TRACE) && FA_TRACE == 2
-                                // development only: time the completion of this Q K^T on the issuing thread
-                                mbar_wait(bar_s_full + 8 * i, (tile + 1 - range[i].lo) & 1, abort_flag);
-                                FA_TR(25 + 10 * i);
-#endif
                             }
+                            FA_TR(24 + 10 * i);
                         }
-                        if (fail) break;
+                    }
+                    if (leader) {
                         umma_commit(bar_v_empty + 8 * st);
                         if (more) umma_commit(bar_k_empty + 8 * st1);
                     }
-                } while (false);
-            }
+                }
+            } while (false);
         }
     } else {
         if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
@@ -459,8 +469,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const uint32_t tmem_p = tmem_s;                          // P (16-bit, two per column) over S[0,64)
         const uint32_t tmem_o = tmem_base + C::kTmemO + qi * D;  // O accumulator, D fp32 columns
         const uint32_t my_s_full = bar_s_full + 8 * qi;
-        const uint32_t my_p_full = bar_p_full + 8 * qi;
-        const uint32_t my_p_part = bar_p_part + 8 * qi;
         const uint32_t my_o_full = bar_o_full + 8 * qi;
         float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
         float l_sum = 0.0f;
@@ -488,6 +496,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             return bits;
         };
         uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(0) : 0u;
+        int owed_part = 0, owed_full = 0;  // named-barrier arrivals posted so far
 
         for (int j = 0; j < n_tiles; ++j) {
             const int cb = t_lo + j;
@@ -625,8 +634,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         // the first kSplitSteps*16 columns are stored: let the MMA warp start P V on them
                         tmem_wait_st();
                         tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(my_p_part);
+                        named_arrive(1 + 2 * qi);
+                        ++owed_part;
                     }
                 }
             };
@@ -636,11 +645,14 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();
             tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(my_p_full);
+            named_arrive(2 + 2 * qi);
+            ++owed_full;
             FA_TR(7);
             if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
         }
+        // a thread that left the loop early still posts the arrivals the MMA warp may be waiting for
+        for (; owed_part < n_tiles; ++owed_part) named_arrive(1 + 2 * qi);
+        for (; owed_full < n_tiles; ++owed_full) named_arrive(2 + 2 * qi);
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
         bool have_o = false;
