@@ -636,6 +636,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         tc_fence_before_sync();
                         named_arrive(1 + 2 * qi);
                         ++owed_part;
+                        FA_TR(8);
                     }
                 }
             };
