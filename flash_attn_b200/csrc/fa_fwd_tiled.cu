@@ -60,8 +60,14 @@ struct Cfg {
     // NQ = 2 rounds the helper warps up to a full warpgroup so that registers can be
     // moved from it to the softmax warpgroups (setmaxnreg works on whole warpgroups).
     static constexpr int kThreads = NQ == 2 ? 384 : 192;
+    // Register hand-over (setmaxnreg): the CTA owns kThreads * kRegsLaunch registers from launch on
+    // and nothing more; an increase that asks for more than the helpers released would block
+    // forever, hence the static_assert.
+    static constexpr int kRegsLaunch = 168;   // what ptxas allots per thread under __launch_bounds__(384, 1)
     static constexpr int kRegsHelper = 48;    // producer / MMA warpgroup after the hand-over
     static constexpr int kRegsSoftmax = 224;  // softmax warpgroups after the hand-over
+    static_assert(NQ == 1 || 256 * kRegsSoftmax + 128 * kRegsHelper <= kThreads * kRegsLaunch,
+                  "register hand-over exceeds the CTA's allocation");
     static constexpr int kProducerWarp = NQ * 4;
     static constexpr int kMmaWarp = NQ * 4 + 1;
     static constexpr int kStages = (D == 64) ? (NQ == 2 ? 3 : 2) : (NQ == 2 ? 2 : 1);
@@ -160,8 +166,8 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
 // Hardware named barriers carry the P hand-over: the 128 threads of a softmax warpgroup
 // arrive (non-blocking), the MMA warp syncs.  Waking from a named barrier costs tens of
 // cycles, while a poll of a shared-memory mbarrier took several hundred whenever the tensor
-// pipe was streaming operands.  A named barrier cannot time out, so a softmax thread that
-// leaves its loop early still posts every arrival it owes (see the end of its loop).
+// pipe was streaming operands.  A named barrier cannot time out, so a softmax warp whose
+// mbarrier wait gave up keeps walking its tile loop and posts every arrival it owes.
 constexpr int kPBarrierThreads = 160;  // 128 softmax threads + the MMA warp
 __device__ __forceinline__ void named_arrive(int id) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kPBarrierThreads) : "memory");
@@ -496,7 +502,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             return bits;
         };
         uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(0) : 0u;
-        int owed_part = 0, owed_full = 0;  // named-barrier arrivals posted so far
 
         for (int j = 0; j < n_tiles; ++j) {
             const int cb = t_lo + j;
@@ -508,14 +513,14 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
             const bool tile_masked_pre = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
             FA_TR(1);
-#if defined(FA_TRACE) && FA_TRACE == 2
-            {   // development only: count the polls lane 0 needs
-                int polls = 0;
-                if (lane == 0) { while (!mbar_test_wait(my_s_full, j & 1) && polls < 100000000) ++polls; }
-                FA_TR(100000 + polls);
+            if (fail != 0 || !mbar_wait_warp(my_s_full, j & 1, abort_flag)) {
+                // a wait gave up: keep the barrier protocol alive (the MMA warp counts on two
+                // arrivals per tile from every softmax thread) and do nothing else
+                fail = 8;
+                named_arrive(1 + 2 * qi);
+                named_arrive(2 + 2 * qi);
+                continue;
             }
-#endif
-            if (!mbar_wait_warp(my_s_full, j & 1, abort_flag)) { fail = 8; break; }
             FA_TR(2);
             tc_fence_after_sync();
 
@@ -635,7 +640,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         tmem_wait_st();
                         tc_fence_before_sync();
                         named_arrive(1 + 2 * qi);
-                        ++owed_part;
+                        FA_TR(8);
                         FA_TR(8);
                     }
                 }
@@ -647,13 +652,9 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tmem_wait_st();
             tc_fence_before_sync();
             named_arrive(2 + 2 * qi);
-            ++owed_full;
             FA_TR(7);
             if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
         }
-        // a thread that left the loop early still posts the arrivals the MMA warp may be waiting for
-        for (; owed_part < n_tiles; ++owed_part) named_arrive(1 + 2 * qi);
-        for (; owed_full < n_tiles; ++owed_full) named_arrive(2 + 2 * qi);
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
         bool have_o = false;
