@@ -92,12 +92,15 @@ int validate(const fa_fwd_params* p) {
     if (p->batch < 1 || p->heads < 1 || p->seqlen_q < 1 || p->seqlen_k < 1 || p->head_dim < 1) return FA_ERR_INVALID_ARG;
     if (p->dtype != FA_DTYPE_FP16 && p->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
     if (p->o_dtype != p->dtype && p->o_dtype != FA_DTYPE_FP32) return FA_ERR_UNSUPPORTED;
-    if (p->head_dim > 128 || p->head_dim % 8 != 0) return FA_ERR_UNSUPPORTED;
+    if (p->head_dim > 128) return FA_ERR_UNSUPPORTED;
     if (!(p->softmax_scale > 0.0f) || !std::isfinite(p->softmax_scale)) return FA_ERR_INVALID_ARG;
     if (!(p->p_dropout >= 0.0f) || !(p->p_dropout < 1.0f)) return FA_ERR_INVALID_ARG;
     if (p->window_left < -1 || p->window_right < -1 || p->num_splits < 0) return FA_ERR_INVALID_ARG;
+    // rows are 16-byte multiples when head_dim % 8 == 0 (TMA reads them in place); otherwise the
+    // tensors are copied to a padded pitch first and only element alignment is needed
+    const uintptr_t align_mask = (p->head_dim % 8 == 0) ? 15u : 3u;
     if ((reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k) | reinterpret_cast<uintptr_t>(p->v) |
-         reinterpret_cast<uintptr_t>(p->o)) & 15u)
+         reinterpret_cast<uintptr_t>(p->o)) & align_mask)
         return FA_ERR_INVALID_ARG;
     const long long units = static_cast<long long>(p->batch) * p->heads;
     const long long tr = (p->seqlen_q + kTile - 1) / kTile;
@@ -166,6 +169,24 @@ size_t partial_bytes(const fa_fwd_params* p, int splits, size_t* lse_off) {
     return o_bytes + ((rows * sizeof(float) + 255) & ~static_cast<size_t>(255));
 }
 
+// head_dim that is not a multiple of 8: Q/K/V are copied to a pitch of d8 = ceil8(head_dim)
+// elements (zero columns), the kernels run on the padded problem, O is copied back.
+struct PadPlan {
+    int d8;
+    size_t q_bytes, kv_bytes, o_bytes, total;
+};
+PadPlan pad_plan(const fa_fwd_params* p) {
+    PadPlan pl;
+    auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+    pl.d8 = (p->head_dim + 7) / 8 * 8;
+    const size_t units = static_cast<size_t>(p->batch) * p->heads;
+    pl.q_bytes = up(units * p->seqlen_q * pl.d8 * 2);
+    pl.kv_bytes = up(units * p->seqlen_k * pl.d8 * 2);
+    pl.o_bytes = up(units * p->seqlen_q * pl.d8 * (p->o_dtype == FA_DTYPE_FP32 ? 4 : 2));
+    pl.total = pl.q_bytes + 2 * pl.kv_bytes + pl.o_bytes;
+    return pl;
+}
+
 }  // namespace
 
 extern "C" {
@@ -176,7 +197,7 @@ const char* fa_strerror(int code) {
     switch (code) {
         case FA_OK: return "success";
         case FA_ERR_INVALID_ARG: return "invalid argument";
-        case FA_ERR_UNSUPPORTED: return "unsupported dtype or head_dim (need fp16/bf16, head_dim % 8 == 0, <= 128)";
+        case FA_ERR_UNSUPPORTED: return "unsupported dtype or head_dim (need fp16/bf16 inputs, head_dim <= 128)";
         case FA_ERR_WORKSPACE: return "workspace missing or too small (see fa_fwd_workspace_bytes)";
         case FA_ERR_CUDA: return "CUDA call failed";
         case FA_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
@@ -218,8 +239,16 @@ int fa_fwd_resolve_splits(const fa_fwd_params* p) {
 
 size_t fa_fwd_workspace_bytes(const fa_fwd_params* p) {
     const int s = fa_fwd_resolve_splits(p);
-    if (s <= 1) return 0;
-    return partial_bytes(p, s, nullptr);
+    if (s < 1) return 0;
+    size_t bytes = 0;
+    if (p->head_dim % 8 != 0) {
+        fa_fwd_params q = *p;
+        q.head_dim = pad_plan(p).d8;
+        bytes = pad_plan(p).total + (s > 1 ? partial_bytes(&q, s, nullptr) : 0);
+    } else if (s > 1) {
+        bytes = partial_bytes(p, s, nullptr);
+    }
+    return bytes;
 }
 
 int fa_fwd(const fa_fwd_params* p) {
@@ -230,10 +259,35 @@ int fa_fwd(const fa_fwd_params* p) {
     if (rc != FA_OK) return rc;
     if (major != 10) return FA_ERR_NOT_SM100;
     const int splits = resolve_splits(p, sms);
-    FwdArgs a;
-    fill_args(p, splits, &a);
     const int units = p->batch * p->heads;
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
+    if (p->head_dim % 8 != 0) {
+        // padded pitch: re-pitch Q, K, V into the workspace, run on head_dim = d8, re-pitch O back
+        const PadPlan pl = pad_plan(p);
+        fa_fwd_params q = *p;
+        q.head_dim = pl.d8;
+        const size_t part = splits > 1 ? partial_bytes(&q, splits, nullptr) : 0;
+        if (!p->workspace || p->workspace_bytes < pl.total + part) return FA_ERR_WORKSPACE;
+        if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return FA_ERR_INVALID_ARG;
+        char* ws = static_cast<char*>(p->workspace);
+        char* qp = ws; char* kp = qp + pl.q_bytes; char* vp = kp + pl.kv_bytes; char* op = vp + pl.kv_bytes;
+        const long long rq = static_cast<long long>(units) * p->seqlen_q, rk = static_cast<long long>(units) * p->seqlen_k;
+        if (launch_repitch(p->q, qp, 2, rq, p->head_dim, pl.d8, stream) != cudaSuccess ||
+            launch_repitch(p->k, kp, 2, rk, p->head_dim, pl.d8, stream) != cudaSuccess ||
+            launch_repitch(p->v, vp, 2, rk, p->head_dim, pl.d8, stream) != cudaSuccess)
+            return FA_ERR_CUDA;
+        q.q = qp; q.k = kp; q.v = vp; q.o = op;
+        q.num_splits = splits;
+        q.workspace = part ? op + pl.o_bytes : nullptr;
+        q.workspace_bytes = part;
+        rc = fa_fwd(&q);
+        if (rc != FA_OK) return rc;
+        if (launch_repitch(op, p->o, p->o_dtype == FA_DTYPE_FP32 ? 4 : 2, rq, pl.d8, p->head_dim, stream) != cudaSuccess)
+            return FA_ERR_CUDA;
+        return FA_OK;
+    }
+    FwdArgs a;
+    fill_args(p, splits, &a);
     if (splits > 1) {
         size_t lse_off = 0;
         const size_t need = partial_bytes(p, splits, &lse_off);
@@ -370,7 +424,7 @@ int fa_fwd_host(const fa_fwd_params* p) {
     probe.heads = static_cast<int>(per);
     const int splits = fa_fwd_resolve_splits(&probe);
     if (splits < 1) return splits;
-    const size_t ws_bytes = splits > 1 ? fa_fwd_workspace_bytes(&probe) : 0;
+    const size_t ws_bytes = fa_fwd_workspace_bytes(&probe);
     const size_t slot = align(q_unit * per) + 2 * align(kv_unit * per) + align(o_unit * per) + align(lse_unit * per) +
                         align(sizeof(float) * per) + align(ws_bytes) + align(sizeof(int));
     if (st.bytes < 2 * slot) {

@@ -84,6 +84,19 @@ __global__ void cast_kernel(const float* src, void* dst, int o_dtype, long long 
     if (i < n) store_out(dst, o_dtype, i, src[i]);
 }
 
+// Row-pitch change for head dims that are not a multiple of 8 (TMA needs 16-byte row
+// strides): [rows, d_src] -> [rows, d_dst], zero-filling new columns / dropping extra ones.
+// This replaces the reference's scalar zero-padding loader (include/utils.h:85-114) by a
+// separate memory-bound pass.
+template <typename T>
+__global__ void repitch_kernel(const T* src, T* dst, long long rows, int d_src, int d_dst) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= rows * d_dst) return;
+    const long long r = i / d_dst;
+    const int c = static_cast<int>(i - r * d_dst);
+    dst[i] = c < d_src ? src[r * d_src + c] : T(0);
+}
+
 // keep[unit, row, col] for the geometry in `a` (same map as the tiled kernel).
 __global__ void dropout_mask_kernel(const FwdArgs a, uint8_t* keep, long long total) {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -142,6 +155,19 @@ cudaError_t launch_cast(const float* src, void* dst, int o_dtype, long long n, c
     if (n <= 0) return cudaSuccess;
     const int threads = 256;
     cast_kernel<<<static_cast<unsigned>((n + threads - 1) / threads), threads, 0, stream>>>(src, dst, o_dtype, n);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_repitch(const void* src, void* dst, int elem_bytes, long long rows, int d_src, int d_dst,
+                           cudaStream_t stream) {
+    const long long total = rows * d_dst;
+    if (total <= 0) return cudaSuccess;
+    const int threads = 256;
+    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+    if (elem_bytes == 2)
+        repitch_kernel<uint16_t><<<blocks, threads, 0, stream>>>(static_cast<const uint16_t*>(src), static_cast<uint16_t*>(dst), rows, d_src, d_dst);
+    else
+        repitch_kernel<uint32_t><<<blocks, threads, 0, stream>>>(static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), rows, d_src, d_dst);
     return cudaGetLastError();
 }
 

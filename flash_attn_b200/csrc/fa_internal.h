@@ -68,6 +68,8 @@ cudaError_t launch_combine(const CombineArgs& a, long long units, cudaStream_t s
 cudaError_t launch_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int part_dtype,
                          long long rows, int d, cudaStream_t stream);
 cudaError_t launch_cast(const float* src, void* dst, int o_dtype, long long n, cudaStream_t stream);
+cudaError_t launch_repitch(const void* src, void* dst, int elem_bytes, long long rows, int d_src, int d_dst,
+                           cudaStream_t stream);
 cudaError_t launch_dropout_mask(const FwdArgs& a, uint8_t* keep, long long units, cudaStream_t stream);
 
 }  // namespace fa

@@ -36,7 +36,7 @@ extern "C" {
  * (the reference's CUDA_CHECK, src/main.cu:18-25, calls exit(1)). */
 #define FA_OK 0
 #define FA_ERR_INVALID_ARG (-1)    /* NULL pointer, non-positive size, bad enum, misaligned pointer */
-#define FA_ERR_UNSUPPORTED (-2)    /* head_dim > 128 or not a multiple of 8, dtype combination     */
+#define FA_ERR_UNSUPPORTED (-2)    /* head_dim > 128, dtype combination                            */
 #define FA_ERR_WORKSPACE (-3)      /* workspace missing or smaller than fa_fwd_workspace_bytes()   */
 #define FA_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed                            */
 #define FA_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait gave up (read from *status)       */
@@ -59,7 +59,8 @@ typedef struct fa_fwd_params {
     int o_dtype;              /* same as dtype, or FA_DTYPE_FP32 */
     int batch, heads;
     int seqlen_q, seqlen_k;   /* the reference has one N for both (param.N) */
-    int head_dim;             /* multiple of 8, <= 128                              (param.d) */
+    int head_dim;             /* <= 128; multiples of 8 are read in place by TMA, other values go
+                                 through a padded copy in the workspace            (param.d) */
     float softmax_scale;      /* > 0                                    (param.softmax_scale) */
     int is_causal;            /* masks k_pos > q_pos      (template flag Is_causal, main.cu:45) */
     int window_left;          /* masks q_pos - k_pos > window_left;  -1 = off (window_size_left)  */
@@ -89,7 +90,7 @@ typedef struct fa_fwd_params {
  * Asynchronous on p->stream. */
 int fa_fwd(const fa_fwd_params* p);
 
-/* Bytes of workspace fa_fwd needs for p (0 when it will not split).
+/* Bytes of workspace fa_fwd needs for p (0 when it neither splits nor pads head_dim).
  * Replaces the cudaMalloc sizing of O_tmp/L/M at src/main.cu:160-162. */
 size_t fa_fwd_workspace_bytes(const fa_fwd_params* p);
 

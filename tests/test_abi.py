@@ -76,9 +76,11 @@ def test_error_paths_without_a_gpu(lib):
     p.softmax_scale = 1.0
     p.window_left = p.window_right = -1
     assert lib.fa_fwd(ctypes.byref(p)) == -2           # head_dim > 128
-    p.head_dim = 60
-    assert lib.fa_fwd(ctypes.byref(p)) == -2           # not a multiple of 8
+    p.head_dim = 60                                     # not a multiple of 8: served through a padded copy
+    p.num_splits = 1
+    assert lib.fa_fwd_workspace_bytes(ctypes.byref(p)) == 4 * ((128 * 64 * 2 + 255) // 256) * 256
     p.head_dim = 64
+    p.num_splits = 0
     p.dtype = 2
     assert lib.fa_fwd(ctypes.byref(p)) == -2           # fp32 inputs
     p.dtype = p.o_dtype = 0

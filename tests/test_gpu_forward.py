@@ -93,6 +93,15 @@ def test_head_dims_below_the_tile(d):
     gpu_util.assert_close(gpu_util.run_case(1, 2, 200, 200, d, "float16", seed=14, causal=True), f"d={d}")
 
 
+def test_head_dims_that_are_not_multiples_of_8():
+    # the reference's default launch: fp16 [1,8,1021,31] -> fp32 O (src/main.cu:39-42); served by a padded copy
+    gpu_util.assert_close(gpu_util.run_case(1, 8, 1021, 1021, 31, "float16", seed=24, out_dtype=torch.float32),
+                          "reference default shape")
+    gpu_util.assert_close(gpu_util.run_case(2, 2, 300, 500, 20, "bfloat16", seed=25, causal=True, q_pos0=200,
+                                            p_dropout=0.1, num_splits=2), "d=20 causal dropout split")
+    gpu_util.assert_close(gpu_util.run_case(1, 3, 1, 900, 100, "bfloat16", seed=26, num_splits=3), "d=100 decode")
+
+
 @pytest.mark.parametrize("splits", [2, 3, 4])
 def test_split_kv_and_combine(splits):
     gpu_util.assert_close(gpu_util.run_case(1, 2, 256, 1024, 64, "float16", seed=15, num_splits=splits),
@@ -135,7 +144,7 @@ def test_argument_errors():
     q = torch.zeros(1, 1, 128, 136, dtype=torch.float16, device="cuda")
     with pytest.raises(_lib.FaError) as e:
         fa.flash_attn_forward(q, q, q)
-    assert e.value.code == -2
+    assert e.value.code == -2  # head_dim > 128
     q = torch.zeros(1, 1, 128, 64, dtype=torch.float16, device="cuda")
     with pytest.raises(_lib.FaError) as e:
         fa.flash_attn_forward(q, q, q, softmax_scale=-1.0)

@@ -50,6 +50,7 @@ def test_reference_kernel_mask_equals_the_stateless_map(case):
     dict(B=2, H=2, N=512, d=128, causal=True),
     dict(B=1, H=2, N=384, d=128, causal=False, window=(128, 128)),
     dict(B=1, H=4, N=256, d=64, causal=False, split_num=2),
+    dict(B=1, H=2, N=256, d=31, causal=True),   # head_dim of the reference's default launch (zero-padded to 32 there)
 ])
 def test_outputs_match_the_reference_kernels(case):
     import flash_attn_b200 as fa
