@@ -14,7 +14,7 @@ FA_OK = 0
 #: every symbol include/fa_b200.h declares
 EXPORTS = ["fa_fwd", "fa_fwd_workspace_bytes", "fa_fwd_resolve_splits", "fa_num_splits_heuristic",
            "fa_dropout_mask", "fa_merge_partial", "fa_cast_output", "fa_fwd_host", "fa_fwd_host_release",
-           "fa_fwd_static_scratch", "fa_static_scratch_bytes", "fa_strerror", "fa_version"]
+           "fa_fwd_static_scratch", "fa_static_scratch_bytes", "fa_launch_reference_params", "fa_strerror", "fa_version"]
 
 
 class FwdParams(ctypes.Structure):
@@ -38,6 +38,18 @@ class FwdParams(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("stream", ctypes.c_void_p),
     ]
+
+
+class RefKernelParams(ctypes.Structure):
+    """struct fa_ref_kernel_params: the reference's mykernelParamType, field for field"""
+    _fields_ = [("Q", ctypes.c_void_p), ("K", ctypes.c_void_p), ("V", ctypes.c_void_p), ("O", ctypes.c_void_p),
+                ("O_tmp", ctypes.c_void_p), ("L", ctypes.c_void_p), ("M", ctypes.c_void_p),
+                ("N", ctypes.c_int), ("d", ctypes.c_int), ("Br", ctypes.c_int), ("Bc", ctypes.c_int),
+                ("Tr", ctypes.c_int), ("Tc", ctypes.c_int),
+                ("softmax_scale", ctypes.c_float), ("dropout_prob", ctypes.c_float),
+                ("seed", ctypes.c_ulonglong), ("states", ctypes.c_void_p),
+                ("window_size_left", ctypes.c_int), ("window_size_right", ctypes.c_int),
+                ("alibi_slopes_ptr", ctypes.c_void_p), ("split_num", ctypes.c_int)]
 
 
 class FaError(RuntimeError):
@@ -69,6 +81,9 @@ def load():
     L.fa_fwd_static_scratch.restype = ctypes.c_int
     L.fa_static_scratch_bytes.argtypes = []
     L.fa_static_scratch_bytes.restype = ctypes.c_size_t
+    L.fa_launch_reference_params.argtypes = [ctypes.POINTER(RefKernelParams)] + [ctypes.c_int] * 6 + [
+        ctypes.c_ulonglong, ctypes.c_void_p]
+    L.fa_launch_reference_params.restype = ctypes.c_int
     L.fa_fwd_workspace_bytes.argtypes = [pp]
     L.fa_fwd_workspace_bytes.restype = ctypes.c_size_t
     L.fa_fwd_resolve_splits.argtypes = [pp]

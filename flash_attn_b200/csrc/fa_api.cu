@@ -369,6 +369,8 @@ struct HostStage {
     void* buf = nullptr;
     size_t bytes = 0;
     cudaStream_t streams[2] = {nullptr, nullptr};
+    void* shim_ws = nullptr;   // workspace of fa_launch_reference_params
+    size_t shim_bytes = 0;
 };
 std::mutex g_stage_mutex;
 HostStage g_stage[64];
@@ -383,14 +385,56 @@ void fa_fwd_host_release(void) {
     cudaGetDevice(&prev);
     for (int d = 0; d < 64; ++d) {
         HostStage& st = g_stage[d];
-        if (!st.buf && !st.streams[0]) continue;
+        if (!st.buf && !st.streams[0] && !st.shim_ws) continue;
         cudaSetDevice(d);
         if (st.buf) cudaFree(st.buf);
+        if (st.shim_ws) cudaFree(st.shim_ws);
         for (auto& s : st.streams) if (s) { cudaStreamDestroy(s); s = nullptr; }
         st.buf = nullptr;
         st.bytes = 0;
+        st.shim_ws = nullptr;
+        st.shim_bytes = 0;
     }
     cudaSetDevice(prev);
+}
+
+int fa_launch_reference_params(const fa_ref_kernel_params* param, int heads, int batch, int is_dropout,
+                               int is_causal, int is_local, int has_alibi, unsigned long long dropout_seed,
+                               void* stream) {
+    if (!param) return FA_ERR_INVALID_ARG;
+    fa_fwd_params p;
+    std::memset(&p, 0, sizeof(p));
+    p.q = param->Q; p.k = param->K; p.v = param->V; p.o = param->O;
+    p.dtype = FA_DTYPE_FP16;
+    p.o_dtype = FA_DTYPE_FP32;
+    p.batch = batch; p.heads = heads;
+    p.seqlen_q = p.seqlen_k = param->N;
+    p.head_dim = param->d;
+    p.softmax_scale = param->softmax_scale;
+    p.is_causal = is_causal ? 1 : 0;
+    p.window_left = is_local ? param->window_size_left : -1;
+    p.window_right = is_local ? param->window_size_right : -1;
+    p.alibi_slopes = has_alibi ? param->alibi_slopes_ptr : nullptr;
+    p.p_dropout = is_dropout ? param->dropout_prob : 0.0f;
+    p.seed = dropout_seed;
+    p.num_splits = param->split_num > 0 ? param->split_num : 1;
+    p.stream = stream;
+    const size_t need = fa_fwd_workspace_bytes(&p);
+    if (need) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FA_ERR_CUDA;
+        std::lock_guard<std::mutex> lock(g_stage_mutex);
+        HostStage& st = g_stage[dev];
+        if (st.shim_bytes < need) {
+            // the old buffer may still be in use by an earlier launch on another stream
+            if (st.shim_ws) { cudaDeviceSynchronize(); cudaFree(st.shim_ws); st.shim_ws = nullptr; st.shim_bytes = 0; }
+            if (cudaMalloc(&st.shim_ws, need) != cudaSuccess) return FA_ERR_CUDA;
+            st.shim_bytes = need;
+        }
+        p.workspace = st.shim_ws;
+        p.workspace_bytes = st.shim_bytes;
+    }
+    return fa_fwd(&p);
 }
 
 int fa_fwd_host(const fa_fwd_params* p) {

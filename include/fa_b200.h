@@ -128,6 +128,36 @@ int fa_fwd_host(const fa_fwd_params* p);
 /* Frees the staging buffers fa_fwd_host cached. */
 void fa_fwd_host_release(void);
 
+/* Field-for-field mirror of the reference's kernel argument block mykernelParamType
+ * (include/utils.h:21-44), for callers that already fill that struct. */
+typedef struct fa_ref_kernel_params {
+    void* Q;                  /* half*  [B,H,N,d] */
+    void* K;
+    void* V;
+    float* O;                 /* float* [B,H,N,d]: the reference writes fp32 */
+    float* O_tmp;             /* split buffers of the reference: not used (the shim keeps its own workspace) */
+    float* L;
+    float* M;
+    int N, d, Br, Bc, Tr, Tc;
+    float softmax_scale;
+    float dropout_prob;
+    unsigned long long seed;  /* declared but never read by the reference kernels */
+    void* states;             /* curandStatePhilox4_32_10_t*: not used, dropout is stateless here */
+    int window_size_left, window_size_right;
+    float* alibi_slopes_ptr;
+    int split_num;
+} fa_ref_kernel_params;
+
+/* Launch described the reference's way: its argument block, its grid (heads = gridDim.y, batch
+ * = gridDim.z, src/main.cu:142) and the template flags of forward_kernel<Is_dropout, Is_causal,
+ * Is_local, Has_alibi, ...> (src/main.cu:147-155) as run-time ints.  dropout_seed is the seed the
+ * caller gave init_curand_states (src/main.cu:135).  fp16 in, fp32 out, any N, any d <= 128.
+ * Runs fa_fwd underneath; the workspace it needs (split partials, padded copies for d % 8 != 0)
+ * is allocated on first use and cached per device (released by fa_fwd_host_release). */
+int fa_launch_reference_params(const fa_ref_kernel_params* param, int heads, int batch, int is_dropout,
+                               int is_causal, int is_local, int has_alibi, unsigned long long dropout_seed,
+                               void* stream);
+
 /* Size of the built-in scratch of fa_fwd_static_scratch. */
 #define FA_STATIC_SCRATCH_BYTES (32u << 20)
 

@@ -63,3 +63,41 @@ def test_outputs_match_the_reference_kernels(case):
                                  num_splits=case.get("split_num", 1))
     err = (o - o_ref).abs()
     assert err.max().item() <= gpu_util.O_MAX_ABS and err.mean().item() <= gpu_util.O_MEAN_ABS, (err.max(), err.mean())
+
+
+def test_launch_with_the_reference_parameter_block():
+    """fa_launch_reference_params takes the reference's own argument struct and flags: the run of the
+    reference's default main() (fp16 [1,8,1021,31], fp32 O, src/main.cu:39-42) against the oracle, and a
+    causal + dropout launch against the reference kernels' own result."""
+    import ctypes
+    from flash_attn_b200 import _lib
+    L = _lib.load()
+
+    def launch(q, k, v, o, N, d, scale, p=0.0, causal=0, seed=0, split=1):
+        prm = _lib.RefKernelParams()
+        prm.Q, prm.K, prm.V, prm.O = q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr()
+        prm.N, prm.d, prm.Br, prm.Bc = N, d, 128, 128
+        prm.Tr = prm.Tc = (N + 127) // 128
+        prm.softmax_scale, prm.dropout_prob = scale, p
+        prm.window_size_left = prm.window_size_right = -1
+        prm.split_num = split
+        _lib.check(L.fa_launch_reference_params(ctypes.byref(prm), q.shape[1], q.shape[0], int(p > 0), causal, 0, 0,
+                                                seed, torch.cuda.current_stream().cuda_stream), "shim")
+        torch.cuda.synchronize()
+
+    B, H, N, d = 1, 8, 1021, 31
+    qn, kn, vn = synth.qkv(41, B, H, N, N, d, "float16")
+    q, k, v = (gpu_util.to_dev(x, "float16") for x in (qn, kn, vn))
+    o = torch.zeros(B, H, N, d, dtype=torch.float32, device="cuda")
+    launch(q, k, v, o, N, d, 1 / np.sqrt(d))
+    want, _ = oracle_lib.forward(qn, kn, vn, 1 / np.sqrt(d))
+    err = np.abs(o.cpu().numpy() - want)
+    assert err.max() <= gpu_util.O_MAX_ABS and err.mean() <= gpu_util.O_MEAN_ABS
+
+    B, H, N, d = 2, 2, 512, 128
+    q, k, v = (gpu_util.to_dev(x, "float16") for x in synth.qkv(42, B, H, N, N, d, "float16"))
+    o = torch.zeros(B, H, N, d, dtype=torch.float32, device="cuda")
+    launch(q, k, v, o, N, d, d ** -0.5, p=0.1, causal=1, seed=48)
+    o_ref, _, _ = ref_gpu.forward(q, k, v, d ** -0.5, causal=True, p_dropout=0.1, seed=48)
+    err = (o - o_ref).abs()
+    assert err.max().item() <= gpu_util.O_MAX_ABS and err.mean().item() <= gpu_util.O_MEAN_ABS
