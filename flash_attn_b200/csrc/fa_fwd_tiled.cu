@@ -270,6 +270,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int lane = threadIdx.x & 31;
 #ifdef FA_TRACE
     int tr_n = 0;
+    FA_TR(90);
 #endif
 
     // ---- which query tiles does this CTA own ------------------------------------
@@ -300,7 +301,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int n_union = hi > lo ? hi - lo : 0;  // KV tiles streamed by this CTA: [lo, hi)
 
     // ---- set-up ----------------------------------------------------------------
-    if (threadIdx.x == 0) {
+    // The producer lane initialises the barriers and immediately puts the Q tiles and the first
+    // ring-full of K/V tiles in flight, so that the HBM latency of these first loads overlaps the
+    // TMEM allocation and the CTA-wide synchronisation instead of following them.
+    int prefilled = 0;  // K/V tiles whose loads were issued during set-up (producer lane only)
+    if (warp == C::kProducerWarp && lane == 0) {
         *abort_flag = 0;
         mbar_init(bar_q_full, 1);
         for (int i = 0; i < NQ; ++i) {
@@ -314,15 +319,40 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(bar_v_empty + 8 * s, 1);
         }
         mbar_fence_init();
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        if (n_union > 0) {
+            int q_tiles = 0;
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
+            mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) {
+                if (range[i].hi > range[i].lo) {
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
+                                    (qb * NQ + i) * kTile, unit);
+                }
+            }
+            prefilled = min(C::kStages, n_union);
+            for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
+                const int row = (lo + t) * kTile;
+                mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
+#pragma unroll
+                for (int b = 0; b < C::kBoxes; ++b)
+                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, unit);
+                mbar_expect_tx(bar_v_full + 8 * t, C::kTileBytes);
+#pragma unroll
+                for (int b = 0; b < C::kBoxes; ++b)
+                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, unit);
+            }
+        }
     }
     if (warp == C::kMmaWarp && n_union > 0) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish();
-    }
-    if (warp == C::kProducerWarp && lane == 0) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -340,20 +370,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (n_union > 0 && warp == C::kProducerWarp) {
             // ======================= TMA producer ===================================
             if (lane == 0) {
-                int q_tiles = 0;
-#pragma unroll
-                for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
-                mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
-#pragma unroll
-                for (int i = 0; i < NQ; ++i) {
-                    if (range[i].hi > range[i].lo) {
-#pragma unroll
-                        for (int b = 0; b < C::kBoxes; ++b)
-                            tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
-                                        (qb * NQ + i) * kTile, unit);
-                    }
-                }
-                for (int t = 0; t < n_union; ++t) {
+                for (int t = prefilled; t < n_union; ++t) {
                     const int st = t % C::kStages;
                     const uint32_t ph = (t / C::kStages) & 1;
                     const int row = (lo + t) * kTile;
@@ -657,6 +674,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
+        FA_TR(91);
         bool have_o = false;
         if (n_tiles > 0 && fail == 0) {
             if (mbar_wait_warp(my_o_full, 0, abort_flag)) { tc_fence_after_sync(); have_o = true; }
@@ -722,8 +740,10 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const long long t0 = clock64();
         while (clock64() - t0 < 200000) { }
     }
+    FA_TR(98);
     tc_fence_before_sync();
     __syncthreads();
+    FA_TR(99);
     if (warp == C::kMmaWarp && n_union > 0) {
         __syncwarp();
         tc_fence_after_sync();
