@@ -80,7 +80,7 @@ struct Cfg {
     static constexpr int kSmemK = NQ * kTileBytes;
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
     static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
-    static constexpr int kNumBars = 2 + 3 * NQ + 4 * kStages;
+    static constexpr int kNumBars = 1 + 2 * NQ + 4 * kStages;
     static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
 };
 
@@ -242,54 +242,6 @@ __device__ __forceinline__ void issue_pv_rest(uint32_t d_tmem, uint32_t a_tmem, 
                  : "memory");
 }
 
-// One unit of work of the persistent kernel: NQ consecutive query tiles of one (batch, head)
-// unit, optionally one KV split of them.
-template <int NQ>
-struct WorkItem {
-    int unit, qb, split;
-    int lo, n_union;       // KV tiles streamed for the item: [lo, lo + n_union)
-    TileRange range[NQ];   // KV tiles of each query tile
-};
-
-// Position k of the launch order -> work item.  unit_group > 1 (causal launches without a left
-// window, where the cost grows with the query block): all units' heaviest query block first,
-// then the next one, ...; otherwise unit-major, which keeps CTAs that run at the same time on
-// the same K/V tiles in L2.
-template <int NQ>
-__device__ __forceinline__ WorkItem<NQ> decode_item(const FwdArgs& a, int k) {
-    const int trq = (a.tr + NQ - 1) / NQ;
-    const int per_unit = trq * a.num_splits;
-    WorkItem<NQ> w;
-    int bx;
-    if (a.unit_group > 1) {
-        bx = k / a.units;
-        w.unit = k - bx * a.units;
-    } else {
-        w.unit = k / per_unit;
-        bx = k - w.unit * per_unit;
-    }
-    w.split = bx % a.num_splits;
-    w.qb = bx / a.num_splits;
-    if (a.is_causal) w.qb = trq - 1 - w.qb;  // heaviest query blocks first
-    int lo = 0x7fffffff, hi = 0;
-#pragma unroll
-    for (int i = 0; i < NQ; ++i) {
-        w.range[i] = kv_tile_range(a, w.qb * NQ + i, w.split);
-        if (w.range[i].hi > w.range[i].lo) {
-            lo = min(lo, w.range[i].lo);
-            hi = max(hi, w.range[i].hi);
-        }
-    }
-    w.n_union = hi > lo ? hi - lo : 0;
-    w.lo = w.n_union > 0 ? lo : 0;
-    return w;
-}
-
-// Persistent kernel: gridDim.x CTAs (one per SM with NQ = 2, two with NQ = 1) walk the work
-// items of the launch; round m gives CTA j item m*G + j, or m*G + (G-1-j) in odd rounds of a
-// heaviest-first order (boustrophedon: close to longest-job-first without any global counter).
-// TMEM, the barriers and the K/V ring live for the whole kernel, so the first loads and S = Q K^T
-// of the next item overlap the epilogue of the current one.
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 __global__ void __launch_bounds__(Cfg<D, NQ>::kThreads, NQ == 1 ? 2 : 1)
 fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -304,12 +256,10 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t sV = smem_base + C::kSmemV;
     const uint32_t bar0 = smem_base + C::kSmemBar;
     // barrier map
-    const uint32_t bar_q_full = bar0;                            // Q tiles of an item have landed
-    const uint32_t bar_q_free = bar0 + 8;                        // the item's last Q K^T has read them
-    const uint32_t bar_s_full = bar0 + 16;                       // [NQ] S_i ready
-    const uint32_t bar_o_full = bar_s_full + 8 * NQ;             // [NQ] O_i of an item complete
-    const uint32_t bar_o_free = bar_o_full + 8 * NQ;             // [NQ] the epilogue has read O_i
-    const uint32_t bar_k_full = bar_o_free + 8 * NQ;             // [kStages]
+    const uint32_t bar_q_full = bar0;
+    const uint32_t bar_s_full = bar0 + 8;                        // [NQ]
+    const uint32_t bar_o_full = bar_s_full + 8 * NQ;             // [NQ]
+    const uint32_t bar_k_full = bar_o_full + 8 * NQ;             // [kStages]
     const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_empty = bar_v_full + 8 * C::kStages;    // [kStages]
@@ -323,29 +273,44 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     FA_TR(90);
 #endif
 
-    // ---- the items of this CTA ---------------------------------------------------
+    // ---- which query tiles does this CTA own ------------------------------------
     const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
-    const int total_items = a.units * trq * a.num_splits;
-    const int G = static_cast<int>(gridDim.x);
-    const bool snake = a.unit_group > 1;
-    auto item_index = [&](int m) -> int {
-        const int pos = (snake && (m & 1)) ? G - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
-        return m * G + pos;
-    };
+    const int per_unit = trq * a.num_splits;
+    // CTA order: groups of unit_group units; inside a group all units' first query block, then
+    // all second ones, ...  With a causal mask the blocks are visited heaviest first, so the
+    // grid is close to a longest-job-first schedule while the K/V working set of the CTAs in
+    // flight (one group) stays far below the L2 size.
+    const int unit0 = (blockIdx.x / (a.unit_group * per_unit)) * a.unit_group;
+    const int gsize = min(a.unit_group, a.units - unit0);
+    const int rem = blockIdx.x - unit0 * per_unit;
+    const int unit = unit0 + rem % gsize;
+    const int bx = rem / gsize;
+    const int split = bx % a.num_splits;
+    int qb = bx / a.num_splits;
+    if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
+    TileRange range[NQ];
+    int lo = 0x7fffffff, hi = 0;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+        range[i] = kv_tile_range(a, qb * NQ + i, split);
+        if (range[i].hi > range[i].lo) {
+            lo = min(lo, range[i].lo);
+            hi = max(hi, range[i].hi);
+        }
+    }
+    const int n_union = hi > lo ? hi - lo : 0;  // KV tiles streamed by this CTA: [lo, hi)
 
     // ---- set-up ----------------------------------------------------------------
-    // The producer lane initialises the barriers and immediately puts the first item's Q tiles and
-    // a ring-full of its K/V tiles in flight, so that their HBM latency overlaps the TMEM
-    // allocation and the CTA-wide synchronisation.
-    int prefilled = -1;  // K/V tiles of the first item issued during set-up (producer lane only)
+    // The producer lane initialises the barriers and immediately puts the Q tiles and the first
+    // ring-full of K/V tiles in flight, so that the HBM latency of these first loads overlaps the
+    // TMEM allocation and the CTA-wide synchronisation instead of following them.
+    int prefilled = 0;  // K/V tiles whose loads were issued during set-up (producer lane only)
     if (warp == C::kProducerWarp && lane == 0) {
         *abort_flag = 0;
         mbar_init(bar_q_full, 1);
-        mbar_init(bar_q_free, 1);
         for (int i = 0; i < NQ; ++i) {
             mbar_init(bar_s_full + 8 * i, 1);
             mbar_init(bar_o_full + 8 * i, 1);
-            mbar_init(bar_o_free + 8 * i, 4);  // one arrival per softmax warp
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(bar_k_full + 8 * s, 1);
@@ -357,43 +322,42 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
-        const WorkItem<NQ> w = decode_item<NQ>(a, item_index(0));
-        if (w.n_union > 0) {
+        if (n_union > 0) {
             int q_tiles = 0;
 #pragma unroll
-            for (int i = 0; i < NQ; ++i) q_tiles += (w.range[i].hi > w.range[i].lo) ? 1 : 0;
+            for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
             mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
 #pragma unroll
             for (int i = 0; i < NQ; ++i) {
-                if (w.range[i].hi > w.range[i].lo) {
+                if (range[i].hi > range[i].lo) {
 #pragma unroll
                     for (int b = 0; b < C::kBoxes; ++b)
                         tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
-                                    (w.qb * NQ + i) * kTile, w.unit);
+                                    (qb * NQ + i) * kTile, unit);
                 }
             }
-            prefilled = min(C::kStages, w.n_union);
+            prefilled = min(C::kStages, n_union);
             for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
-                const int row = (w.lo + t) * kTile;
+                const int row = (lo + t) * kTile;
                 mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
 #pragma unroll
                 for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, w.unit);
+                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, unit);
                 mbar_expect_tx(bar_v_full + 8 * t, C::kTileBytes);
 #pragma unroll
                 for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, w.unit);
+                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, unit);
             }
         }
     }
-    if (warp == C::kMmaWarp) {
+    if (warp == C::kMmaWarp && n_union > 0) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = (n_union > 0) ? *tmem_slot : 0u;
 
     int fail = 0;
 
@@ -403,59 +367,28 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // covers one whole branch below.
     if (warp >= NQ * 4) {
         if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsHelper));
-        if (warp == C::kProducerWarp) {
+        if (n_union > 0 && warp == C::kProducerWarp) {
             // ======================= TMA producer ===================================
             if (lane == 0) {
-                int kv_slot = 0;  // K/V tiles pushed into the ring so far
-                int item_n = 0;   // non-empty items started so far
-                for (int m = 0; m * G < total_items && fail == 0; ++m) {
-                    const int k = item_index(m);
-                    if (k >= total_items) continue;
-                    const WorkItem<NQ> w = decode_item<NQ>(a, k);
-                    if (w.n_union == 0) continue;
-                    int t0 = 0;
-                    if (m == 0 && prefilled >= 0) {
-                        t0 = prefilled;  // Q and the first tiles of this item went out during set-up
-                    } else {
-                        // the previous item's last Q K^T must have read the Q tiles
-                        if (item_n > 0 && !mbar_wait(bar_q_free, (item_n - 1) & 1, abort_flag)) { fail = 1; break; }
-                        int q_tiles = 0;
+                for (int t = prefilled; t < n_union; ++t) {
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int row = (lo + t) * kTile;
+                    if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
+                    FA_TR(10);
+                    mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
 #pragma unroll
-                        for (int i = 0; i < NQ; ++i) q_tiles += (w.range[i].hi > w.range[i].lo) ? 1 : 0;
-                        mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, unit);
+                    if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
+                    FA_TR(11);
+                    mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
 #pragma unroll
-                        for (int i = 0; i < NQ; ++i) {
-                            if (w.range[i].hi > w.range[i].lo) {
-#pragma unroll
-                                for (int b = 0; b < C::kBoxes; ++b)
-                                    tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
-                                                (w.qb * NQ + i) * kTile, w.unit);
-                            }
-                        }
-                    }
-                    for (int t = t0; t < w.n_union; ++t) {
-                        const int slot = kv_slot + t;
-                        const int st = slot % C::kStages;
-                        const uint32_t ph = (slot / C::kStages) & 1;
-                        const int row = (w.lo + t) * kTile;
-                        if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
-                        FA_TR(10);
-                        mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
-#pragma unroll
-                        for (int b = 0; b < C::kBoxes; ++b)
-                            tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, w.unit);
-                        if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
-                        FA_TR(11);
-                        mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
-#pragma unroll
-                        for (int b = 0; b < C::kBoxes; ++b)
-                            tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, w.unit);
-                    }
-                    kv_slot += w.n_union;
-                    ++item_n;
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, unit);
                 }
             }
-        } else if (warp == C::kMmaWarp) {
+        } else if (n_union > 0 && warp == C::kMmaWarp) {
             // ======================= MMA issuer =====================================
             // The warp walks the loop together (it meets the softmax warpgroups at named
             // barriers); one elected lane issues the MMAs and commits.
@@ -482,40 +415,28 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 issue_pv_rest(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
                               v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv);
             };
-            int kv_slot = 0;            // K/V tiles consumed so far
-            int item_n = 0;             // non-empty items started so far
-            int o_items[NQ] = {};       // items in which query tile i had work, so far
-            for (int m = 0; m * G < total_items && fail == 0; ++m) {
-                const int k = item_index(m);
-                if (k >= total_items) continue;
-                const WorkItem<NQ> w = decode_item<NQ>(a, k);
-                if (w.n_union == 0) continue;
-                auto active = [&](int i, int tile) { return tile >= w.range[i].lo && tile < w.range[i].hi; };
-                if (!mbar_wait_warp(bar_q_full, item_n & 1, abort_flag)) { fail = 3; break; }
-                {
-                    const int st = kv_slot % C::kStages;
-                    if (!mbar_wait_warp(bar_k_full + 8 * st, (kv_slot / C::kStages) & 1, abort_flag)) { fail = 4; break; }
-                    tc_fence_after_sync();
-                    if (leader) {
+            auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
+            do {
+                if (!mbar_wait_warp(bar_q_full, 0, abort_flag)) { fail = 3; break; }
+                if (!mbar_wait_warp(bar_k_full, 0, abort_flag)) { fail = 4; break; }
+                tc_fence_after_sync();
+                if (leader) {
 #pragma unroll
-                        for (int i = 0; i < NQ; ++i) {
-                            if (active(i, w.lo)) {
-                                issue_qk(i, st);
-                                umma_commit(bar_s_full + 8 * i);
-                            }
+                    for (int i = 0; i < NQ; ++i) {
+                        if (active(i, lo)) {
+                            issue_qk(i, 0);
+                            umma_commit(bar_s_full + 8 * i);
                         }
-                        umma_commit(bar_k_empty + 8 * st);
-                        if (w.n_union == 1) umma_commit(bar_q_free);
                     }
+                    umma_commit(bar_k_empty);
                 }
-                for (int t = 0; t < w.n_union && fail == 0; ++t) {
-                    const int tile = w.lo + t;
-                    const int slot = kv_slot + t;
-                    const int st = slot % C::kStages;
-                    const uint32_t ph = (slot / C::kStages) & 1;
-                    const int st1 = (slot + 1) % C::kStages;
-                    const uint32_t ph1 = ((slot + 1) / C::kStages) & 1;
-                    const bool more = t + 1 < w.n_union;
+                for (int t = 0; t < n_union && fail == 0; ++t) {
+                    const int tile = lo + t;
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int st1 = (t + 1) % C::kStages;
+                    const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
+                    const bool more = t + 1 < n_union;
                     // K/V tiles arrive long before they are needed; their barriers are looked at now,
                     // while the warp would wait for P anyway
                     if (!mbar_wait_warp(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
@@ -527,20 +448,16 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < NQ; ++i) {
                         if (active(i, tile)) {
-                            if (tile == w.range[i].lo && o_items[i] > 0) {
-                                // the epilogue of the previous item must have read O_i before it is overwritten
-                                if (!mbar_wait_warp(bar_o_free + 8 * i, (o_items[i] - 1) & 1, abort_flag)) { fail = 5; break; }
-                            }
                             // P V starts on the first three quarters of P while the last is exponentiated
                             named_sync(1 + 2 * i);
                             FA_TR(21 + 10 * i);
                             tc_fence_after_sync();
-                            if (leader) issue_pv_a(i, st, tile > w.range[i].lo ? 1u : 0u);
+                            if (leader) issue_pv_a(i, st, tile > range[i].lo ? 1u : 0u);
                             named_sync(2 + 2 * i);
                             tc_fence_after_sync();
                             if (leader) {
                                 issue_pv_b(i, st);
-                                if (tile == w.range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
+                                if (tile == range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
                             }
                             FA_TR(22 + 10 * i);
                         }
@@ -552,287 +469,263 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             FA_TR(24 + 10 * i);
                         }
                     }
-                    if (fail) break;
                     if (leader) {
                         umma_commit(bar_v_empty + 8 * st);
                         if (more) umma_commit(bar_k_empty + 8 * st1);
-                        if (more && t + 2 == w.n_union) umma_commit(bar_q_free);  // the item's last Q K^T is queued
                     }
                 }
-                kv_slot += w.n_union;
-                ++item_n;
-#pragma unroll
-                for (int i = 0; i < NQ; ++i) o_items[i] += (w.range[i].hi > w.range[i].lo) ? 1 : 0;
-            }
+            } while (false);
         }
     } else {
         if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
         // ======================= softmax / epilogue =============================
         const int qi = warp >> 2;                        // which query tile of the CTA
+        const int rb = qb * NQ + qi;                     // its 128-row block inside the unit
         const int r = threadIdx.x & 127;                 // row inside the tile
+        const int row = rb * kTile + r;                  // row inside the unit
+        const long long qpos = a.q_pos0 + row;
+        const TileRange mine_r = (qi == 0) ? range[0] : range[NQ - 1];
+        const int t_lo = mine_r.lo;
+        const int n_tiles = mine_r.hi - mine_r.lo;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem_base + qi * kTile;          // S accumulator, 128 fp32 columns
         const uint32_t tmem_p = tmem_s;                          // P (16-bit, two per column) over S[0,64)
         const uint32_t tmem_o = tmem_base + C::kTmemO + qi * D;  // O accumulator, D fp32 columns
         const uint32_t my_s_full = bar_s_full + 8 * qi;
         const uint32_t my_o_full = bar_o_full + 8 * qi;
-        const uint32_t my_o_free = bar_o_free + 8 * qi;
+        float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
+        float l_sum = 0.0f;
+        float slope2 = 0.0f;
+        if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
         // every unmasked key lies at or before the query: |q - k| = q - k
         const bool keys_not_after = a.is_causal || a.window_right == 0;
+        unsigned long long subseq = 0;
+        if constexpr (kDropout)
+            subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
+                     static_cast<unsigned long long>(rb * a.num_splits + split);
         const float scale2 = a.scale_log2;
-        int s_cnt = 0;  // KV tiles this query tile has processed so far (parity of s_full)
-        int o_cnt = 0;  // items in which this query tile had work so far (parity of o_full)
+        // Dropout keep bits of this row for KV tile j of this query tile: bit 2*g + w <-> columns
+        // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
+        // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
+        // tile ahead, while the warp would otherwise wait for S.
+        auto tile_keep_bits = [&](int j) -> uint32_t {
+            if constexpr (!kDropout) return 0xffffffffu;
+            uint32_t mine = 0;
+            if (lane < 16) mine = philox_keep4(a.drop, subseq, 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
+            const int half = (lane >> 3) & 1;
+            uint32_t bits = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
+            return bits;
+        };
+        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(0) : 0u;
 
-        for (int m = 0; m * G < total_items; ++m) {
-            const int k_item = item_index(m);
-            if (k_item >= total_items) continue;
-            const WorkItem<NQ> w = decode_item<NQ>(a, k_item);
-            const int unit = w.unit;
-            const int split = w.split;
-            const int rb = w.qb * NQ + qi;                   // the tile's 128-row block inside the unit
-            const int row = rb * kTile + r;                  // row inside the unit
-            const long long qpos = a.q_pos0 + row;
-            const TileRange mine_r = (qi == 0) ? w.range[0] : w.range[NQ - 1];
-            const int t_lo = mine_r.lo;
-            const int n_tiles = mine_r.hi - mine_r.lo;
-            float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
-            float l_sum = 0.0f;
-            float slope2 = 0.0f;
-            if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
-            unsigned long long subseq = 0;
-            if constexpr (kDropout)
-                subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
-                         static_cast<unsigned long long>(rb * a.num_splits + split);
-            // Dropout keep bits of this row for KV tile j of this query tile: bit 2*g + w <-> columns
-            // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
-            // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
-            // tile ahead, while the warp would otherwise wait for S.
-            auto tile_keep_bits = [&](int j) -> uint32_t {
-                if constexpr (!kDropout) return 0xffffffffu;
-                uint32_t mine = 0;
-                if (lane < 16) mine = philox_keep4(a.drop, subseq, 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
-                const int half = (lane >> 3) & 1;
-                uint32_t bits = 0;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
-                return bits;
-            };
-            uint32_t keep_next = (n_tiles > 0 && fail == 0) ? tile_keep_bits(0) : 0u;
-
-            for (int j = 0; j < n_tiles; ++j, ++s_cnt) {
-                const int cb = t_lo + j;
-                const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
-                // columns this row may attend to inside the tile: [c_lo, c_hi] (worked out before S arrives)
-                int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
-                if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
-                if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
-                if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
-                const bool tile_masked = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
-                FA_TR(1);
-                if (fail != 0 || !mbar_wait_warp(my_s_full, s_cnt & 1, abort_flag)) {
-                    // a wait gave up: keep the barrier protocol alive (the MMA warp counts on two
-                    // arrivals per tile from every softmax thread) and do nothing else
-                    fail = 8;
-                    named_arrive(1 + 2 * qi);
-                    named_arrive(2 + 2 * qi);
-                    continue;
-                }
-                FA_TR(2);
-                tc_fence_after_sync();
-
-                float s[128];
-                {
-                    uint32_t tmp[4][32];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_base + c * 32, tmp[c]);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int c = 0; c < 128; ++c) s[c] = __uint_as_float(tmp[c / 32][c % 32]);
-                }
-                FA_TR(3);
-
-                if (tile_masked) {
-#pragma unroll
-                    for (int c = 0; c < 128; ++c)
-                        if (c < c_lo || c > c_hi) s[c] = -INFINITY;
-                }
-
-                // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
-                // (softmax_scale > 0) and the scale is folded into the exponent's FMA.
-                float m_tile;
-                if constexpr (kAlibi) {
-                    const float dist0 = static_cast<float>(qpos - kbase);
-                    if (keys_not_after) {
-                        const float base = -slope2 * dist0;
-#pragma unroll
-                        for (int c = 0; c < 128; ++c) s[c] = fmaf(s[c], scale2, fmaf(slope2, static_cast<float>(c), base));
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 128; ++c) s[c] = fmaf(-slope2, fabsf(dist0 - static_cast<float>(c)), s[c] * scale2);
-                    }
-                }
-                {
-                    float mx[4] = {s[0], s[1], s[2], s[3]};
-#pragma unroll
-                    for (int c = 4; c < 128; c += 8) {
-                        mx[0] = max3(mx[0], s[c], s[c + 1]);
-                        mx[1] = max3(mx[1], s[c + 2], s[c + 3]);
-                        if (c + 4 < 128) {
-                            mx[2] = max3(mx[2], s[c + 4], s[c + 5]);
-                            mx[3] = max3(mx[3], s[c + 6], s[c + 7]);
-                        }
-                    }
-                    m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-                    if constexpr (!kAlibi) m_tile *= scale2;
-                }
-                FA_TR(4);
-
-                // lazy rescale: keep the old reference max unless the new one is much larger
-                float m_new = m_ref;
-                float factor = 1.0f;
-                if (m_tile > m_ref + kRescaleThreshold || m_ref == -INFINITY) {
-                    m_new = fmaxf(m_ref, m_tile);
-                    factor = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
-                }
-                const bool rescale = (j > 0) && (m_new != m_ref);
-                if (__any_sync(0xffffffffu, rescale)) {
-                    // P V of the previous tile has completed (its commit precedes s_full), so O is stable.
-                    const float f = rescale ? factor : 1.0f;
-#pragma unroll 1
-                    for (int c = 0; c < D / 16; ++c) {  // small chunks: the score row stays in registers meanwhile
-                        uint32_t orow[16];
-                        tmem_ld16(tmem_o + lane_base + c * 16, orow);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
-                        tmem_st16(tmem_o + lane_base + c * 16, orow);
-                    }
-                }
-                l_sum *= (m_new != m_ref) ? factor : 1.0f;
-                m_ref = m_new;
-                const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-                const uint32_t keep_bits = keep_next;
-                FA_TR(5);
-
-                // P = exp2(s*scale - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
-                float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-                const float2 neg_m2 = make_float2(neg_m, neg_m);
-                const float2 scale22 = make_float2(scale2, scale2);
-                // On tiles without masked elements (every score finite, so no argument is -inf) pairs
-                // kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.
-                auto exp_tile = [&](auto poly_tag) {
-                    constexpr int kPolyFrom = decltype(poly_tag)::value;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {  // quarters of 32 columns
-                        uint32_t pr[16];
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
-                            uint32_t msk = 0xffffffffu;
-                            if constexpr (kDropout) {
-                                const uint32_t two = (keep_bits >> (2 * (c * 4 + g))) & 3u;
-                                msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
-                            }
-#pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const int col = c * 32 + g * 8 + q * 2;
-                                float2 x = make_float2(s[col], s[col + 1]);
-                                if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
-                                else x = __ffma2_rn(x, scale22, neg_m2);
-                                float2 p;
-                                if (q >= kPolyFrom) {
-                                    p = poly_exp2_pair(x);
-                                } else {
-                                    p.x = fast_exp2(x.x);
-                                    p.y = fast_exp2(x.y);
-                                }
-                                acc[q] = __fadd2_rn(acc[q], p);
-                                pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
-                            }
-                        }
-                        tmem_st16(tmem_p + lane_base + c * 16, pr);
-                        if (c == (kSplitSteps * 16) / 32 - 1) {
-                            // the first kSplitSteps*16 columns are stored: let the MMA warp start P V on them
-                            tmem_wait_st();
-                            tc_fence_before_sync();
-                            named_arrive(1 + 2 * qi);
-                            FA_TR(8);
-                        }
-                    }
-                };
-                if (tile_masked) exp_tile(std::integral_constant<int, 4>{});
-                else exp_tile(std::integral_constant<int, kPolyPairsFrom>{});
-                FA_TR(6);
-                l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
-                tmem_wait_st();
-                tc_fence_before_sync();
+        for (int j = 0; j < n_tiles; ++j) {
+            const int cb = t_lo + j;
+            const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
+            // columns this row may attend to inside the tile: [c_lo, c_hi] (worked out before S arrives)
+            int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
+            if (a.is_causal) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos - kbase));
+            if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
+            if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
+            const bool tile_masked_pre = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
+            FA_TR(1);
+            if (fail != 0 || !mbar_wait_warp(my_s_full, j & 1, abort_flag)) {
+                // a wait gave up: keep the barrier protocol alive (the MMA warp counts on two
+                // arrivals per tile from every softmax thread) and do nothing else
+                fail = 8;
+                named_arrive(1 + 2 * qi);
                 named_arrive(2 + 2 * qi);
-                FA_TR(7);
-                if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
+                continue;
+            }
+            FA_TR(2);
+            tc_fence_after_sync();
+
+            float s[128];
+            {
+                uint32_t tmp[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_base + c * 32, tmp[c]);
+                tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 128; ++c) s[c] = __uint_as_float(tmp[c / 32][c % 32]);
+            }
+            FA_TR(3);
+
+            const bool tile_masked = tile_masked_pre;
+            if (tile_masked) {
+#pragma unroll
+                for (int c = 0; c < 128; ++c)
+                    if (c < c_lo || c > c_hi) s[c] = -INFINITY;
             }
 
-            // ---- epilogue of the item: normalise and write O, LSE ---------------------
-            FA_TR(91);
-            bool have_o = false;
-            if (n_tiles > 0 && fail == 0) {
-                if (mbar_wait_warp(my_o_full, o_cnt & 1, abort_flag)) { tc_fence_after_sync(); have_o = true; }
-                else fail = 9;
-            }
-            if (n_tiles > 0) ++o_cnt;
-            float inv = 0.0f;
-            if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
-            const bool row_ok = row < a.seqlen_q;
-            const float lse_val = (l_sum > 0.0f) ? (m_ref * kLn2 + __logf(l_sum)) : -INFINITY;
-            const long long unit_ll = unit;
-            if (fail == 0) {
-                if (a.num_splits > 1) {
-                    const long long prow = (unit_ll * a.num_splits + split) * a.seqlen_q + row;
-                    if (row_ok) a.lse_partial[prow] = lse_val;
-                } else if (a.lse != nullptr && row_ok) {
-                    a.lse[unit_ll * a.seqlen_q + row] = lse_val;
+            // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
+            // (softmax_scale > 0) and the scale is folded into the exponent's FMA.
+            float m_tile;
+            if constexpr (kAlibi) {
+                const float dist0 = static_cast<float>(qpos - kbase);
+                if (keys_not_after) {
+                    const float base = -slope2 * dist0;
+#pragma unroll
+                    for (int c = 0; c < 128; ++c) s[c] = fmaf(s[c], scale2, fmaf(slope2, static_cast<float>(c), base));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 128; ++c) s[c] = fmaf(-slope2, fabsf(dist0 - static_cast<float>(c)), s[c] * scale2);
                 }
             }
+            {
+                float mx[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t orow[32];
-                if (have_o) {
+                for (int c = 4; c < 128; c += 8) {
+                    mx[0] = max3(mx[0], s[c], s[c + 1]);
+                    mx[1] = max3(mx[1], s[c + 2], s[c + 3]);
+                    if (c + 4 < 128) {
+                        mx[2] = max3(mx[2], s[c + 4], s[c + 5]);
+                        mx[3] = max3(mx[3], s[c + 6], s[c + 7]);
+                    }
+                }
+                m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+                if constexpr (!kAlibi) m_tile *= scale2;
+            }
+            FA_TR(4);
+
+            // lazy rescale: keep the old reference max unless the new one is much larger
+            float m_new = m_ref;
+            float factor = 1.0f;
+            if (m_tile > m_ref + kRescaleThreshold || m_ref == -INFINITY) {
+                m_new = fmaxf(m_ref, m_tile);
+                factor = (m_ref == -INFINITY) ? 0.0f : fast_exp2(m_ref - m_new);
+            }
+            const bool rescale = (j > 0) && (m_new != m_ref);
+            if (__any_sync(0xffffffffu, rescale)) {
+                // P V of the previous tile has completed (its commit precedes s_full), so O is stable.
+                const float f = rescale ? factor : 1.0f;
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t orow[32];
                     tmem_ld32(tmem_o + lane_base + c * 32, orow);
                     tmem_wait_ld();
-                    if (c == D / 32 - 1) {
-                        // O_i is in registers: the next item's P V may overwrite the accumulator
-                        tc_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(my_o_free);
-                    }
-                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) orow[i] = 0u;
+                    for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * f);
+                    tmem_st32(tmem_o + lane_base + c * 32, orow);
                 }
-                if (!row_ok || fail != 0) continue;
-                const int col0 = c * 32;
-                if (a.num_splits > 1 || a.o_is_fp32) {
-                    float* dst = (a.num_splits > 1)
-                                     ? a.o_partial + ((unit_ll * a.num_splits + split) * a.seqlen_q + row) * a.head_dim
-                                     : static_cast<float*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+            }
+            l_sum *= (m_new != m_ref) ? factor : 1.0f;
+            m_ref = m_new;
+            const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
+            const uint32_t keep_bits = keep_next;
+            FA_TR(5);
+
+            // P = exp2(s*scale - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
+            float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            const float2 neg_m2 = make_float2(neg_m, neg_m);
+            const float2 scale22 = make_float2(scale2, scale2);
+            // On tiles without masked elements (every score finite, so no argument is -inf) pairs
+            // kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.
+            auto exp_tile = [&](auto poly_tag) {
+                constexpr int kPolyFrom = decltype(poly_tag)::value;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        if (col0 + i < a.head_dim) {
-                            float4 v4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
-                                                    __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-                            *reinterpret_cast<float4*>(dst + col0 + i) = v4;
+                for (int c = 0; c < 4; ++c) {  // quarters of 32 columns
+                    uint32_t pr[16];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
+                        uint32_t msk = 0xffffffffu;
+                        if constexpr (kDropout) {
+                            const uint32_t two = (keep_bits >> (2 * (c * 4 + g))) & 3u;
+                            msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int col = c * 32 + g * 8 + q * 2;
+                            float2 x = make_float2(s[col], s[col + 1]);
+                            if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
+                            else x = __ffma2_rn(x, scale22, neg_m2);
+                            float2 p;
+                            if (q >= kPolyFrom) {
+                                p = poly_exp2_pair(x);
+                            } else {
+                                p.x = fast_exp2(x.x);
+                                p.y = fast_exp2(x.y);
+                            }
+                            acc[q] = __fadd2_rn(acc[q], p);
+                            pr[g * 4 + q] = pack2<kBf16>(p.x, p.y) & msk;
                         }
                     }
-                } else {
-                    uint16_t* dst = static_cast<uint16_t*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+                    tmem_st16(tmem_p + lane_base + c * 16, pr);
+                    if (c == (kSplitSteps * 16) / 32 - 1) {
+                        // the first kSplitSteps*16 columns are stored: let the MMA warp start P V on them
+                        tmem_wait_st();
+                        tc_fence_before_sync();
+                        named_arrive(1 + 2 * qi);
+                        FA_TR(8);
+                        FA_TR(8);
+                    }
+                }
+            };
+            if (tile_masked) exp_tile(std::integral_constant<int, 4>{});
+            else exp_tile(std::integral_constant<int, kPolyPairsFrom>{});
+            FA_TR(6);
+            l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
+            tmem_wait_st();
+            tc_fence_before_sync();
+            named_arrive(2 + 2 * qi);
+            FA_TR(7);
+            if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
+        }
+
+        // ---- epilogue: normalise and write O, LSE --------------------------------
+        FA_TR(91);
+        bool have_o = false;
+        if (n_tiles > 0 && fail == 0) {
+            if (mbar_wait_warp(my_o_full, 0, abort_flag)) { tc_fence_after_sync(); have_o = true; }
+            else fail = 9;
+        }
+        float inv = 0.0f;
+        if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
+        const bool row_ok = row < a.seqlen_q;
+        const float lse_val = (l_sum > 0.0f) ? (m_ref * kLn2 + __logf(l_sum)) : -INFINITY;
+        const long long unit_ll = unit;
+        if (a.num_splits > 1) {
+            const long long prow = (unit_ll * a.num_splits + split) * a.seqlen_q + row;
+            if (row_ok) a.lse_partial[prow] = lse_val;
+        } else if (a.lse != nullptr && row_ok) {
+            a.lse[unit_ll * a.seqlen_q + row] = lse_val;
+        }
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        if (col0 + i < a.head_dim) {
-                            uint4 v4;
-                            v4.x = pack2<kBf16>(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
-                            v4.y = pack2<kBf16>(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-                            v4.z = pack2<kBf16>(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
-                            v4.w = pack2<kBf16>(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
-                            *reinterpret_cast<uint4*>(dst + col0 + i) = v4;
-                        }
+        for (int c = 0; c < D / 32; ++c) {
+            uint32_t orow[32];
+            if (have_o) {
+                tmem_ld32(tmem_o + lane_base + c * 32, orow);
+                tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) orow[i] = 0u;
+            }
+            if (!row_ok) continue;
+            const int col0 = c * 32;
+            if (a.num_splits > 1 || a.o_is_fp32) {
+                float* dst = (a.num_splits > 1)
+                                 ? a.o_partial + ((unit_ll * a.num_splits + split) * a.seqlen_q + row) * a.head_dim
+                                 : static_cast<float*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    if (col0 + i < a.head_dim) {
+                        float4 v4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        *reinterpret_cast<float4*>(dst + col0 + i) = v4;
+                    }
+                }
+            } else {
+                uint16_t* dst = static_cast<uint16_t*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    if (col0 + i < a.head_dim) {
+                        uint4 v4;
+                        v4.x = pack2<kBf16>(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
+                        v4.y = pack2<kBf16>(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        v4.z = pack2<kBf16>(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
+                        v4.w = pack2<kBf16>(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + col0 + i) = v4;
                     }
                 }
             }
@@ -851,7 +744,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tc_fence_before_sync();
     __syncthreads();
     FA_TR(99);
-    if (warp == C::kMmaWarp) {
+    if (warp == C::kMmaWarp && n_union > 0) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::kTmemCols);
@@ -873,19 +766,9 @@ cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMa
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     const int trq = (a.tr + NQ - 1) / NQ;
-    const long long items = static_cast<long long>(units) * trq * a.num_splits;
-    if (items <= 0 || items > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    static int sm_count[64] = {};
-    int sms = (dev >= 0 && dev < 64) ? sm_count[dev] : 0;
-    if (sms == 0) {
-        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) sm_count[dev] = sms;
-    }
-    // persistent CTAs: as many as fit the device at once (one per SM with two query tiles per CTA)
-    const long long resident = static_cast<long long>(sms) * (NQ == 1 ? 2 : 1);
-    const unsigned ctas = static_cast<unsigned>(items < resident ? items : resident);
-    kern<<<ctas, Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, a);
+    const long long ctas = static_cast<long long>(units) * trq * a.num_splits;
+    if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    kern<<<static_cast<unsigned>(ctas), Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, a);
     return cudaGetLastError();
 }
 
