@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <cstdlib>
 #include <type_traits>
 #include "fa_internal.h"
 #include "sm100_ptx.cuh"
@@ -57,16 +58,17 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 template <int D, int NQ>
 struct Cfg {
-    // NQ = 2 rounds the helper warps up to a full warpgroup so that registers can be
-    // moved from it to the softmax warpgroups (setmaxnreg works on whole warpgroups).
-    static constexpr int kThreads = NQ == 2 ? 384 : 192;
+    // The helper warps (producer, MMA issuer) are rounded up to a full warpgroup so that registers
+    // can be moved from it to the softmax warpgroups (setmaxnreg works on whole warpgroups).
+    static constexpr int kThreads = NQ == 2 ? 384 : 256;
     // Register hand-over (setmaxnreg): the CTA owns kThreads * kRegsLaunch registers from launch on
     // and nothing more; an increase that asks for more than the helpers released would block
     // forever, hence the static_assert.
-    static constexpr int kRegsLaunch = 168;   // what ptxas allots per thread under __launch_bounds__(384, 1)
-    static constexpr int kRegsHelper = 48;    // producer / MMA warpgroup after the hand-over
-    static constexpr int kRegsSoftmax = 224;  // softmax warpgroups after the hand-over
-    static_assert(NQ == 1 || 256 * kRegsSoftmax + 128 * kRegsHelper <= kThreads * kRegsLaunch,
+    // ptxas allots 168 registers per thread under __launch_bounds__(384, 1) and 128 under (256, 2)
+    static constexpr int kRegsLaunch = NQ == 2 ? 168 : 128;
+    static constexpr int kRegsHelper = NQ == 2 ? 48 : 40;     // producer / MMA warpgroup after the hand-over
+    static constexpr int kRegsSoftmax = NQ == 2 ? 224 : 208;  // softmax warpgroups after the hand-over
+    static_assert(NQ * 128 * kRegsSoftmax + 128 * kRegsHelper <= kThreads * kRegsLaunch,
                   "register hand-over exceeds the CTA's allocation");
     static constexpr int kProducerWarp = NQ * 4;
     static constexpr int kMmaWarp = NQ * 4 + 1;
@@ -361,12 +363,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
     int fail = 0;
 
-    // With NQ = 2 the 384 threads start with 168 registers each; the helper warpgroup
-    // (producer, MMA issuer, two idle warps) hands most of its share to the two softmax
-    // warpgroups, which hold a 128-column score row per thread.  Each register regime
-    // covers one whole branch below.
+    // The helper warpgroup (producer, MMA issuer, two idle warps) hands most of its registers to
+    // the softmax warpgroups, which hold a 128-column score row per thread.  Each register
+    // regime covers one whole branch below.
     if (warp >= NQ * 4) {
-        if constexpr (NQ == 2) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsHelper));
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsHelper));
         if (n_union > 0 && warp == C::kProducerWarp) {
             // ======================= TMA producer ===================================
             if (lane == 0) {
@@ -477,7 +478,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             } while (false);
         }
     } else {
-        if constexpr (NQ == 2) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
         // ======================= softmax / epilogue =============================
         const int qi = warp >> 2;                        // which query tile of the CTA
         const int rb = qb * NQ + qi;                     // its 128-row block inside the unit
@@ -797,7 +798,9 @@ cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUte
     const bool alibi = a.alibi_slopes != nullptr;
     // two query tiles per CTA once a unit has more than one; a single tile (decode-like
     // shapes) keeps two independent CTAs per SM instead
-    const bool pair = a.tr >= 2;
+    // (development switch: FA_B200_PAIR=0 runs one query tile per CTA, two CTAs per SM, throughout)
+    static const bool allow_pair = [] { const char* e = std::getenv("FA_B200_PAIR"); return !(e && e[0] == '0'); }();
+    const bool pair = a.tr >= 2 && allow_pair;
     if (a.head_dim <= 64) {
         return pair ? launch_dtype<64, 2>(a, tq, tk, tv, units, bf16, alibi, dropout, stream)
                     : launch_dtype<64, 1>(a, tq, tk, tv, units, bf16, alibi, dropout, stream);
