@@ -17,6 +17,11 @@
 //       MN-major), accumulators in tensor memory.  With NQ = 2 the two query tiles
 //       alternate on the tensor pipe, so the softmax of one overlaps the MMAs of
 //       the other while both share every K/V tile brought in by TMA.
+// KV tiles are visited from the last to the first (the softmax is order-independent and the
+// dropout draw of an element is a function of its position): with a causal mask the second
+// query tile of a CTA owns one KV tile more than the first, the diagonal one, and walking
+// backwards puts that solo tile at the start, where it overlaps the first tile of the other
+// query tile, instead of at the end, where the other warpgroup would idle.
 // The reference keeps O in shared memory and renormalises it every tile
 // (src/flash_forward.h:248-290); here O stays un-normalised in tensor memory and
 // is divided by the row sum once, in the epilogue.
@@ -340,7 +345,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             prefilled = min(C::kStages, n_union);
             for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
-                const int row = (lo + t) * kTile;
+                const int row = (hi - 1 - t) * kTile;  // KV tiles are walked from the last to the first
                 mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
 #pragma unroll
                 for (int b = 0; b < C::kBoxes; ++b)
@@ -374,7 +379,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 for (int t = prefilled; t < n_union; ++t) {
                     const int st = t % C::kStages;
                     const uint32_t ph = (t / C::kStages) & 1;
-                    const int row = (lo + t) * kTile;
+                    const int row = (hi - 1 - t) * kTile;
                     if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
                     FA_TR(10);
                     mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
@@ -424,7 +429,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (leader) {
 #pragma unroll
                     for (int i = 0; i < NQ; ++i) {
-                        if (active(i, lo)) {
+                        if (active(i, hi - 1)) {
                             issue_qk(i, 0);
                             umma_commit(bar_s_full + 8 * i);
                         }
@@ -432,7 +437,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     umma_commit(bar_k_empty);
                 }
                 for (int t = 0; t < n_union && fail == 0; ++t) {
-                    const int tile = lo + t;
+                    const int tile = hi - 1 - t;
                     const int st = t % C::kStages;
                     const uint32_t ph = (t / C::kStages) & 1;
                     const int st1 = (t + 1) % C::kStages;
@@ -453,16 +458,16 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             named_sync(1 + 2 * i);
                             FA_TR(21 + 10 * i);
                             tc_fence_after_sync();
-                            if (leader) issue_pv_a(i, st, tile > range[i].lo ? 1u : 0u);
+                            if (leader) issue_pv_a(i, st, tile < range[i].hi - 1 ? 1u : 0u);
                             named_sync(2 + 2 * i);
                             tc_fence_after_sync();
                             if (leader) {
                                 issue_pv_b(i, st);
-                                if (tile == range[i].hi - 1) umma_commit(bar_o_full + 8 * i);
+                                if (tile == range[i].lo) umma_commit(bar_o_full + 8 * i);
                             }
                             FA_TR(22 + 10 * i);
                         }
-                        if (more && active(i, tile + 1)) {
+                        if (more && active(i, tile - 1)) {
                             if (leader) {
                                 issue_qk(i, st1);
                                 umma_commit(bar_s_full + 8 * i);
@@ -519,10 +524,10 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
             return bits;
         };
-        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(0) : 0u;
+        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(n_tiles - 1) : 0u;  // argument: tile index from the first KV tile
 
         for (int j = 0; j < n_tiles; ++j) {
-            const int cb = t_lo + j;
+            const int cb = t_lo + n_tiles - 1 - j;  // from the last KV tile of this query tile to the first
             const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
             // columns this row may attend to inside the tile: [c_lo, c_hi] (worked out before S arrives)
             int c_lo = 0, c_hi = min(kTile - 1, a.seqlen_k - 1 - cb * kTile);
@@ -671,7 +676,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_before_sync();
             named_arrive(2 + 2 * qi);
             FA_TR(7);
-            if (j + 1 < n_tiles) keep_next = tile_keep_bits(j + 1);
+            if (j + 1 < n_tiles) keep_next = tile_keep_bits(n_tiles - 2 - j);
         }
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
