@@ -38,12 +38,13 @@ encode_tiled_fn get_encode_tiled() {
 // [units, rows, d] 16-bit tensor, box = 64 elements x 128 rows x 1 unit, 128-byte
 // swizzle; out-of-range rows and columns read as zero, which replaces the
 // reference's hand-written zero padding (include/utils.h:67-114).
-int make_tensor_map(CUtensorMap* m, bool bf16, const void* base, int d, long long rows, long long units) {
+int make_tensor_map(CUtensorMap* m, bool bf16, const void* base, int d, long long rows, long long units,
+                    int box_rows = kTile) {
     encode_tiled_fn enc = get_encode_tiled();
     if (!enc) return FA_ERR_CUDA;
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(units)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(rows) * d * 2};
-    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(kTile), 1};
+    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -157,6 +158,15 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
 bool decode_kernel_enabled() {
     static const bool on = [] {
         const char* e = std::getenv("FA_B200_DECODE");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+// Development switch: FA_B200_TMA_STORE=0 writes O with per-thread global stores throughout.
+bool tma_epilogue_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("FA_B200_TMA_STORE");
         return !(e && e[0] == '0');
     }();
     return on;
@@ -301,6 +311,10 @@ int fa_fwd(const fa_fwd_params* p) {
     if ((rc = make_tensor_map(&tq, bf16, p->q, p->head_dim, p->seqlen_q, units)) != FA_OK) return rc;
     if ((rc = make_tensor_map(&tk, bf16, p->k, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
     if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
+    // 16-bit output of an unsplit launch is written by TMA stores, one 32-row box per warp
+    CUtensorMap to = tq;
+    a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32 && tma_epilogue_enabled()) ? 1 : 0;
+    if (a.o_tma && (rc = make_tensor_map(&to, bf16, p->o, p->head_dim, p->seqlen_q, units, 32)) != FA_OK) return rc;
     if (p->seqlen_q == 1 && decode_kernel_enabled()) {
         // one query row per unit: the streaming kernel with keys on the tensor-memory lanes
         DecodeArgs d;
@@ -313,7 +327,7 @@ int fa_fwd(const fa_fwd_params* p) {
         d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
         d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;
         if (launch_decode(d, tk, tv, units, bf16, stream) != cudaSuccess) return FA_ERR_CUDA;
-    } else if (launch_fwd_tiled(a, tq, tk, tv, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) {
+    } else if (launch_fwd_tiled(a, tq, tk, tv, to, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) {
         return FA_ERR_CUDA;
     }
     if (splits > 1) {

@@ -252,7 +252,8 @@ __device__ __forceinline__ void issue_pv_rest(uint32_t d_tmem, uint32_t a_tmem, 
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 __global__ void __launch_bounds__(Cfg<D, NQ>::kThreads, NQ == 1 ? 2 : 1)
 fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                 const __grid_constant__ CUtensorMap tmap_v, const FwdArgs a) {
+                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+                 const FwdArgs a) {
     using C = Cfg<D, NQ>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles need a 1024-byte aligned base
@@ -697,6 +698,42 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else if (a.lse != nullptr && row_ok) {
             a.lse[unit_ll * a.seqlen_q + row] = lse_val;
         }
+        if (a.o_tma && have_o) {
+            // 16-bit output of an unsplit launch: the rows are staged in this query tile's Q buffer
+            // (free once the last Q K^T has completed, which o_full implies) in the 128-byte-swizzled
+            // box layout, and each warp hands its 32 rows to the TMA unit, which writes whole lines
+            // and clips rows >= seqlen_q and columns >= head_dim.
+            const uint32_t stage = sQ + qi * C::kTileBytes;
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t orow[32];
+                tmem_ld32(tmem_o + lane_base + c * 32, orow);
+                tmem_wait_ld();
+                const uint32_t row_addr = stage + (c >> 1) * (kTile * 128) + r * 128;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    const uint32_t x = pack2<kBf16>(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
+                    const uint32_t y = pack2<kBf16>(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                    const uint32_t z = pack2<kBf16>(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
+                    const uint32_t w = pack2<kBf16>(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
+                    const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + (i >> 3)) ^ static_cast<uint32_t>(r & 7);
+                    st_shared_v4(row_addr + chunk * 16, x, y, z, w);
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                const int y0 = rb * kTile + (warp & 3) * 32;
+                if (y0 < a.seqlen_q) {
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        if (b * 64 < a.head_dim)
+                            tma_store_3d(&tmap_o, stage + b * (kTile * 128) + (warp & 3) * (32 * 128), b * 64, y0, unit);
+                    tma_store_commit();
+                    tma_store_wait_read();
+                }
+            }
+        } else {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
             uint32_t orow[32];
@@ -736,6 +773,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
             }
         }
+        }
     }
 
     // ---- teardown ------------------------------------------------------------------
@@ -759,7 +797,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                       int units, cudaStream_t stream) {
+                       const CUtensorMap& to, int units, cudaStream_t stream) {
     auto kern = fwd_tiled_kernel<D, NQ, kBf16, kAlibi, kDropout>;
     constexpr int smem = Cfg<D, NQ>::kSmemBytes;
     static bool configured[64] = {};
@@ -774,32 +812,32 @@ cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMa
     const int trq = (a.tr + NQ - 1) / NQ;
     const long long ctas = static_cast<long long>(units) * trq * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    kern<<<static_cast<unsigned>(ctas), Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, a);
+    kern<<<static_cast<unsigned>(ctas), Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, to, a);
     return cudaGetLastError();
 }
 
 template <int D, int NQ, bool kBf16>
 cudaError_t launch_flags(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         int units, bool alibi, bool dropout, cudaStream_t stream) {
+                         const CUtensorMap& to, int units, bool alibi, bool dropout, cudaStream_t stream) {
     if (alibi) {
-        return dropout ? launch_one<D, NQ, kBf16, true, true>(a, tq, tk, tv, units, stream)
-                       : launch_one<D, NQ, kBf16, true, false>(a, tq, tk, tv, units, stream);
+        return dropout ? launch_one<D, NQ, kBf16, true, true>(a, tq, tk, tv, to, units, stream)
+                       : launch_one<D, NQ, kBf16, true, false>(a, tq, tk, tv, to, units, stream);
     }
-    return dropout ? launch_one<D, NQ, kBf16, false, true>(a, tq, tk, tv, units, stream)
-                   : launch_one<D, NQ, kBf16, false, false>(a, tq, tk, tv, units, stream);
+    return dropout ? launch_one<D, NQ, kBf16, false, true>(a, tq, tk, tv, to, units, stream)
+                   : launch_one<D, NQ, kBf16, false, false>(a, tq, tk, tv, to, units, stream);
 }
 
 template <int D, int NQ>
 cudaError_t launch_dtype(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         int units, bool bf16, bool alibi, bool dropout, cudaStream_t stream) {
-    return bf16 ? launch_flags<D, NQ, true>(a, tq, tk, tv, units, alibi, dropout, stream)
-                : launch_flags<D, NQ, false>(a, tq, tk, tv, units, alibi, dropout, stream);
+                         const CUtensorMap& to, int units, bool bf16, bool alibi, bool dropout, cudaStream_t stream) {
+    return bf16 ? launch_flags<D, NQ, true>(a, tq, tk, tv, to, units, alibi, dropout, stream)
+                : launch_flags<D, NQ, false>(a, tq, tk, tv, to, units, alibi, dropout, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                             int units, bool bf16, bool dropout, cudaStream_t stream) {
+                             const CUtensorMap& to, int units, bool bf16, bool dropout, cudaStream_t stream) {
     const bool alibi = a.alibi_slopes != nullptr;
     // two query tiles per CTA once a unit has more than one; a single tile (decode-like
     // shapes) keeps two independent CTAs per SM instead
@@ -807,11 +845,11 @@ cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUte
     static const bool allow_pair = [] { const char* e = std::getenv("FA_B200_PAIR"); return !(e && e[0] == '0'); }();
     const bool pair = a.tr >= 2 && allow_pair;
     if (a.head_dim <= 64) {
-        return pair ? launch_dtype<64, 2>(a, tq, tk, tv, units, bf16, alibi, dropout, stream)
-                    : launch_dtype<64, 1>(a, tq, tk, tv, units, bf16, alibi, dropout, stream);
+        return pair ? launch_dtype<64, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream)
+                    : launch_dtype<64, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream);
     }
-    return pair ? launch_dtype<128, 2>(a, tq, tk, tv, units, bf16, alibi, dropout, stream)
-                : launch_dtype<128, 1>(a, tq, tk, tv, units, bf16, alibi, dropout, stream);
+    return pair ? launch_dtype<128, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream)
+                : launch_dtype<128, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream);
 }
 
 }  // namespace fa

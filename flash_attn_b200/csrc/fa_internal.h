@@ -28,12 +28,14 @@ struct FwdArgs {
     int is_causal, window_left, window_right;
     long long q_pos0, k_pos0;
     int o_is_fp32;
+    int o_tma;              // O leaves through the TMA store map (16-bit output, unsplit launch)
     DropoutParams drop;
 };
 
-// Launchers implemented in the .cu files; all return a cudaError_t.
+// Launchers implemented in the .cu files; all return a cudaError_t.  `to` is the store map of O
+// (32-row boxes); it is read only when a.o_tma is set.
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                             int units, bool bf16, bool dropout, cudaStream_t stream);
+                             const CUtensorMap& to, int units, bool bf16, bool dropout, cudaStream_t stream);
 
 // Device-side argument block of the decode kernel (seqlen_q = 1).
 struct DecodeArgs {
