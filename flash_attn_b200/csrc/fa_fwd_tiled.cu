@@ -34,15 +34,18 @@
 #include "sm100_ptx.cuh"
 
 // Optional timeline tracing for kernel development (compiled out unless FA_TRACE is
-// defined): lane 0 of every warp of CTA 0 records (event, clock) pairs.
+// defined): lane 0 of every warp of CTA FA_TRACE_CTA records (event, clock) pairs.
 #ifdef FA_TRACE
+#ifndef FA_TRACE_CTA
+#define FA_TRACE_CTA 0
+#endif
 __device__ long long fa_trace_buf[16 * 512];
 extern "C" int fa_trace_read(long long* host_out) {
     return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_trace_buf, sizeof(long long) * 16 * 512));
 }
 #define FA_TR(ev)                                                                              \
     do {                                                                                       \
-        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n < 255) {                        \
+        if (blockIdx.x == FA_TRACE_CTA && (threadIdx.x & 31) == 0 && tr_n < 255) {                        \
             fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n] = (ev);                          \
             fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n + 1] = clock64();                 \
             ++tr_n;                                                                            \
@@ -296,6 +299,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int split = bx % a.num_splits;
     int qb = bx / a.num_splits;
     if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
+    FA_TR(94);
     TileRange range[NQ];
     int lo = 0x7fffffff, hi = 0;
 #pragma unroll
@@ -307,6 +311,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
     }
     const int n_union = hi > lo ? hi - lo : 0;  // KV tiles streamed by this CTA: [lo, hi)
+    FA_TR(95);
 
     // ---- set-up ----------------------------------------------------------------
     // The producer lane initialises the barriers and immediately puts the Q tiles and the first
@@ -330,6 +335,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
+        if (a.o_tma) tma_prefetch_desc(&tmap_o);
         if (n_union > 0) {
             int q_tiles = 0;
 #pragma unroll
@@ -362,9 +368,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish();
     }
+    FA_TR(92);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    FA_TR(93);
     const uint32_t tmem_base = (n_union > 0) ? *tmem_slot : 0u;
 
     int fail = 0;
@@ -426,6 +434,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             do {
                 if (!mbar_wait_warp(bar_q_full, 0, abort_flag)) { fail = 3; break; }
                 if (!mbar_wait_warp(bar_k_full, 0, abort_flag)) { fail = 4; break; }
+                FA_TR(26);
                 tc_fence_after_sync();
                 if (leader) {
 #pragma unroll
@@ -687,6 +696,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (mbar_wait_warp(my_o_full, 0, abort_flag)) { tc_fence_after_sync(); have_o = true; }
             else fail = 9;
         }
+        FA_TR(96);
         float inv = 0.0f;
         if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
         const bool row_ok = row < a.seqlen_q;
@@ -704,35 +714,35 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // box layout, and each warp hands its 32 rows to the TMA unit, which writes whole lines
             // and clips rows >= seqlen_q and columns >= head_dim.
             const uint32_t stage = sQ + qi * C::kTileBytes;
+            const int y0 = rb * kTile + (warp & 3) * 32;
 #pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                uint32_t orow[32];
-                tmem_ld32(tmem_o + lane_base + c * 32, orow);
+            for (int b = 0; b < C::kBoxes; ++b) {  // a 64-column box at a time: its store runs while the next is packed
+                uint32_t orow[2][32];
+                tmem_ld32(tmem_o + lane_base + b * 64, orow[0]);
+                tmem_ld32(tmem_o + lane_base + b * 64 + 32, orow[1]);
                 tmem_wait_ld();
-                const uint32_t row_addr = stage + (c >> 1) * (kTile * 128) + r * 128;
+                const uint32_t row_addr = stage + b * (kTile * 128) + r * 128;
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    const uint32_t x = pack2<kBf16>(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
-                    const uint32_t y = pack2<kBf16>(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-                    const uint32_t z = pack2<kBf16>(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
-                    const uint32_t w = pack2<kBf16>(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
-                    const uint32_t chunk = static_cast<uint32_t>((c & 1) * 4 + (i >> 3)) ^ static_cast<uint32_t>(r & 7);
-                    st_shared_v4(row_addr + chunk * 16, x, y, z, w);
+                for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        const uint32_t x = pack2<kBf16>(__uint_as_float(orow[h][i]) * inv, __uint_as_float(orow[h][i + 1]) * inv);
+                        const uint32_t y = pack2<kBf16>(__uint_as_float(orow[h][i + 2]) * inv, __uint_as_float(orow[h][i + 3]) * inv);
+                        const uint32_t z = pack2<kBf16>(__uint_as_float(orow[h][i + 4]) * inv, __uint_as_float(orow[h][i + 5]) * inv);
+                        const uint32_t w = pack2<kBf16>(__uint_as_float(orow[h][i + 6]) * inv, __uint_as_float(orow[h][i + 7]) * inv);
+                        const uint32_t chunk = static_cast<uint32_t>(h * 4 + (i >> 3)) ^ static_cast<uint32_t>(r & 7);
+                        st_shared_v4(row_addr + chunk * 16, x, y, z, w);
+                    }
                 }
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-                const int y0 = rb * kTile + (warp & 3) * 32;
-                if (y0 < a.seqlen_q) {
-#pragma unroll
-                    for (int b = 0; b < C::kBoxes; ++b)
-                        if (b * 64 < a.head_dim)
-                            tma_store_3d(&tmap_o, stage + b * (kTile * 128) + (warp & 3) * (32 * 128), b * 64, y0, unit);
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && y0 < a.seqlen_q && b * 64 < a.head_dim) {
+                    tma_store_3d(&tmap_o, stage + b * (kTile * 128) + (warp & 3) * (32 * 128), b * 64, y0, unit);
                     tma_store_commit();
-                    tma_store_wait_read();
                 }
             }
+            FA_TR(97);
+            if (lane == 0) tma_store_wait_read();
         } else {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
