@@ -455,7 +455,12 @@ def main():
         roof = {"bound": "tensor", "achieved": flops / sec / 1e12, "peak": peaks["tensor"], "unit": "TFLOP/s"}
     roof["frac"] = roof["achieved"] / roof["peak"]
     roof["peak_source"] = peaks["source"] + (" burst" if not is_decode else " copy")
-    roof["traffic"] = None  # DRAM bytes per launch from ncu: see profiles/
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+    # summarised under profiles/: config 2 captured at full size, config 4 captured on 128 of the
+    # 2048 units and scaled by the units processed; null where no capture of the workload exists
+    ncu_traffic = {"c2": 201.42e6 + 47.13e6, "c4": 16 * (2.1476e9 + 5.1e6)}
+    roof["traffic"] = ncu_traffic.get(name) if args.batch is None else None
+    roof["traffic_source"] = "ncu capture (static figure, not measured in this run)" if roof["traffic"] else None
     roof["kernel"] = "decode_kernel (+ combine_kernel)" if is_decode else "fwd_tiled_kernel"
     launches_per_step = 1 if w["splits"] <= 1 else 2
 
