@@ -37,6 +37,7 @@ class FwdParams(ctypes.Structure):
         ("workspace", ctypes.c_void_p), ("workspace_bytes", ctypes.c_size_t),
         ("status", ctypes.c_void_p),
         ("stream", ctypes.c_void_p),
+        ("heads_k", ctypes.c_int),
     ]
 
 

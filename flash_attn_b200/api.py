@@ -19,9 +19,9 @@ _DT = {torch.float16: _lib.FA_DTYPE_FP16, torch.bfloat16: _lib.FA_DTYPE_BF16, to
 def _params(q, k, v, o, lse, softmax_scale, causal, window, alibi_slopes, p_dropout, seed, offset, unit0, num_splits,
             q_pos0, k_pos0):
     B, H, Nq, d = q.shape
-    Nk = k.shape[2]
-    if k.shape != (B, H, Nk, d) or v.shape != (B, H, Nk, d):
-        raise ValueError("k and v must be [batch, heads, seqlen_k, head_dim] matching q")
+    Hk, Nk = k.shape[1], k.shape[2]
+    if k.shape != (B, Hk, Nk, d) or v.shape != (B, Hk, Nk, d) or Hk < 1 or H % Hk != 0:
+        raise ValueError("k and v must be [batch, heads_k, seqlen_k, head_dim] with heads a multiple of heads_k")
     for t in (q, k, v, o):
         if not t.is_contiguous():
             raise ValueError("q, k, v, o must be contiguous [batch, heads, seqlen, head_dim]")
@@ -39,6 +39,7 @@ def _params(q, k, v, o, lse, softmax_scale, causal, window, alibi_slopes, p_drop
     p.p_dropout, p.seed, p.offset, p.unit0 = float(p_dropout), int(seed), int(offset), int(unit0)
     p.num_splits = int(num_splits)
     p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
+    p.heads_k = Hk  # grouped-query attention when Hk < H
     return p
 
 
@@ -47,7 +48,8 @@ def flash_attn_forward(q, k, v, softmax_scale=None, causal=False, window=(-1, -1
                        q_pos0=0, k_pos0=0, unit0=0, workspace=None, status=None):
     """O, LSE = attention(Q, K, V) on the current CUDA device and stream.
 
-    q [B,H,Nq,d], k/v [B,H,Nk,d], fp16 or bf16, contiguous.  `window` = (left,
+    q [B,H,Nq,d], k/v [B,Hk,Nk,d] (Hk divides H; query head h reads K/V head
+    h // (H // Hk)), fp16 or bf16, contiguous.  `window` = (left,
     right) with -1 = unbounded; `alibi_slopes` fp32 [H]; `num_splits` 0 = the
     reference heuristic, 1 = none, n = forced; `q_pos0`/`k_pos0` = global positions
     of row/column 0 (for one block of a sharded sequence).  Returns (o, lse).

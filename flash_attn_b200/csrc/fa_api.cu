@@ -91,6 +91,7 @@ int sm_count_of_current_device(int* sms, int* major) {
 int validate(const fa_fwd_params* p) {
     if (!p || !p->q || !p->k || !p->v || !p->o) return FA_ERR_INVALID_ARG;
     if (p->batch < 1 || p->heads < 1 || p->seqlen_q < 1 || p->seqlen_k < 1 || p->head_dim < 1) return FA_ERR_INVALID_ARG;
+    if (p->heads_k < 0 || (p->heads_k > 0 && p->heads % p->heads_k != 0)) return FA_ERR_INVALID_ARG;
     if (p->dtype != FA_DTYPE_FP16 && p->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
     if (p->o_dtype != p->dtype && p->o_dtype != FA_DTYPE_FP32) return FA_ERR_UNSUPPORTED;
     if (p->head_dim > 128) return FA_ERR_UNSUPPORTED;
@@ -108,6 +109,9 @@ int validate(const fa_fwd_params* p) {
     if (units * tr > 0x3fffffffLL) return FA_ERR_TOO_LARGE;
     return FA_OK;
 }
+
+// K/V heads of the call (heads_k = 0 means one K/V head per query head).
+int kv_heads(const fa_fwd_params* p) { return p->heads_k > 0 ? p->heads_k : p->heads; }
 
 int resolve_splits(const fa_fwd_params* p, int sms) {
     const int tr = (p->seqlen_q + kTile - 1) / kTile;
@@ -129,6 +133,7 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->status = p->status;
     a->heads = p->heads;
     a->units = p->batch * p->heads;
+    a->kv_group = p->heads / kv_heads(p);
     // query blocks of very different cost (causal, no left window): heaviest-first over groups of
     // 16 units; otherwise unit-major, which keeps neighbouring CTAs on the same K/V tiles in L2
     a->unit_group = (p->is_causal && p->window_left < 0) ? 16 : 1;
@@ -191,7 +196,7 @@ PadPlan pad_plan(const fa_fwd_params* p) {
     pl.d8 = (p->head_dim + 7) / 8 * 8;
     const size_t units = static_cast<size_t>(p->batch) * p->heads;
     pl.q_bytes = up(units * p->seqlen_q * pl.d8 * 2);
-    pl.kv_bytes = up(units * p->seqlen_k * pl.d8 * 2);
+    pl.kv_bytes = up(static_cast<size_t>(p->batch) * kv_heads(p) * p->seqlen_k * pl.d8 * 2);
     pl.o_bytes = up(units * p->seqlen_q * pl.d8 * (p->o_dtype == FA_DTYPE_FP32 ? 4 : 2));
     pl.total = pl.q_bytes + 2 * pl.kv_bytes + pl.o_bytes;
     return pl;
@@ -281,7 +286,8 @@ int fa_fwd(const fa_fwd_params* p) {
         if (reinterpret_cast<uintptr_t>(p->workspace) & 255u) return FA_ERR_INVALID_ARG;
         char* ws = static_cast<char*>(p->workspace);
         char* qp = ws; char* kp = qp + pl.q_bytes; char* vp = kp + pl.kv_bytes; char* op = vp + pl.kv_bytes;
-        const long long rq = static_cast<long long>(units) * p->seqlen_q, rk = static_cast<long long>(units) * p->seqlen_k;
+        const long long rq = static_cast<long long>(units) * p->seqlen_q;
+        const long long rk = static_cast<long long>(p->batch) * kv_heads(p) * p->seqlen_k;
         if (launch_repitch(p->q, qp, 2, rq, p->head_dim, pl.d8, stream) != cudaSuccess ||
             launch_repitch(p->k, kp, 2, rk, p->head_dim, pl.d8, stream) != cudaSuccess ||
             launch_repitch(p->v, vp, 2, rk, p->head_dim, pl.d8, stream) != cudaSuccess)
@@ -309,8 +315,9 @@ int fa_fwd(const fa_fwd_params* p) {
     const bool bf16 = p->dtype == FA_DTYPE_BF16;
     CUtensorMap tq, tk, tv;
     if ((rc = make_tensor_map(&tq, bf16, p->q, p->head_dim, p->seqlen_q, units)) != FA_OK) return rc;
-    if ((rc = make_tensor_map(&tk, bf16, p->k, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
-    if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units)) != FA_OK) return rc;
+    const int units_k = p->batch * kv_heads(p);
+    if ((rc = make_tensor_map(&tk, bf16, p->k, p->head_dim, p->seqlen_k, units_k)) != FA_OK) return rc;
+    if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units_k)) != FA_OK) return rc;
     // 16-bit output of an unsplit launch is written by TMA stores, one 32-row box per warp
     CUtensorMap to = tq;
     a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32 && tma_epilogue_enabled()) ? 1 : 0;
@@ -322,7 +329,7 @@ int fa_fwd(const fa_fwd_params* p) {
         d.q = p->q; d.o = p->o; d.lse = p->lse;
         d.o_partial = a.o_partial; d.lse_partial = a.lse_partial;
         d.alibi_slopes = p->alibi_slopes; d.status = p->status;
-        d.heads = p->heads; d.seqlen_k = p->seqlen_k; d.head_dim = p->head_dim; d.tc = a.tc;
+        d.heads = p->heads; d.kv_group = a.kv_group; d.seqlen_k = p->seqlen_k; d.head_dim = p->head_dim; d.tc = a.tc;
         d.num_splits = splits; d.tiles_per_split = a.tiles_per_split; d.scale_log2 = a.scale_log2;
         d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
         d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;
@@ -468,22 +475,26 @@ int fa_fwd_host(const fa_fwd_params* p) {
         if (!s && cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return FA_ERR_CUDA;
 
     const long long units = static_cast<long long>(p->batch) * p->heads;
+    const long long group = p->heads / kv_heads(p);  // query units per K/V unit; slices hold whole groups
+    const long long kunits = units / group;
     const size_t esz = 2, osz = p->o_dtype == FA_DTYPE_FP32 ? 4 : 2;
     const size_t q_unit = static_cast<size_t>(p->seqlen_q) * p->head_dim * esz;
     const size_t kv_unit = static_cast<size_t>(p->seqlen_k) * p->head_dim * esz;
     const size_t o_unit = static_cast<size_t>(p->seqlen_q) * p->head_dim * osz;
     const size_t lse_unit = static_cast<size_t>(p->seqlen_q) * sizeof(float);
     // slices of units, double-buffered so copies in one stream overlap work in the other
-    const long long slices = std::min<long long>(units, 8);
-    const long long per = (units + slices - 1) / slices;
+    const long long slices = std::min<long long>(kunits, 8);
+    const long long per_k = (kunits + slices - 1) / slices;
+    const long long per = per_k * group;
     auto align = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
     fa_fwd_params probe = chk;
     probe.batch = 1;
     probe.heads = static_cast<int>(per);
+    probe.heads_k = static_cast<int>(per_k);
     const int splits = fa_fwd_resolve_splits(&probe);
     if (splits < 1) return splits;
     const size_t ws_bytes = fa_fwd_workspace_bytes(&probe);
-    const size_t slot = align(q_unit * per) + 2 * align(kv_unit * per) + align(o_unit * per) + align(lse_unit * per) +
+    const size_t slot = align(q_unit * per) + 2 * align(kv_unit * per_k) + align(o_unit * per) + align(lse_unit * per) +
                         align(sizeof(float) * per) + align(ws_bytes) + align(sizeof(int));
     if (st.bytes < 2 * slot) {
         if (st.buf) cudaFree(st.buf);
@@ -504,14 +515,14 @@ int fa_fwd_host(const fa_fwd_params* p) {
         char* base = static_cast<char*>(st.buf) + (s & 1) * slot;
         char* dq = base;
         char* dk = dq + align(q_unit * per);
-        char* dv = dk + align(kv_unit * per);
-        char* dout = dv + align(kv_unit * per);
+        char* dv = dk + align(kv_unit * per_k);
+        char* dout = dv + align(kv_unit * per_k);
         char* dlse = dout + align(o_unit * per);
         char* dslopes = dlse + align(lse_unit * per);
         char* dws = dslopes + align(sizeof(float) * per);
         bool ok = cudaMemcpyAsync(dq, static_cast<const char*>(p->q) + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
-        ok = ok && cudaMemcpyAsync(dk, static_cast<const char*>(p->k) + u0 * kv_unit, n * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
-        ok = ok && cudaMemcpyAsync(dv, static_cast<const char*>(p->v) + u0 * kv_unit, n * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(dk, static_cast<const char*>(p->k) + (u0 / group) * kv_unit, (n / group) * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(dv, static_cast<const char*>(p->v) + (u0 / group) * kv_unit, (n / group) * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
         if (ok && p->alibi_slopes)
             ok = cudaMemcpyAsync(dslopes, slopes_by_unit.data() + u0, n * sizeof(float), cudaMemcpyHostToDevice, stream) == cudaSuccess;
         if (!ok) { result = FA_ERR_CUDA; break; }
@@ -520,6 +531,7 @@ int fa_fwd_host(const fa_fwd_params* p) {
         q.lse = p->lse ? reinterpret_cast<float*>(dlse) : nullptr;
         q.batch = 1;
         q.heads = static_cast<int>(n);
+        q.heads_k = static_cast<int>(n / group);
         q.alibi_slopes = p->alibi_slopes ? reinterpret_cast<const float*>(dslopes) : nullptr;
         q.unit0 = p->unit0 + static_cast<uint64_t>(u0);
         q.num_splits = splits;

@@ -93,6 +93,7 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
     const int lane = threadIdx.x & 31;
     const int unit = blockIdx.x / a.num_splits;
     const int split = blockIdx.x - unit * a.num_splits;
+    const int kv_unit = a.kv_group > 1 ? unit / a.kv_group : unit;  // grouped-query attention: K/V head of this unit
 
     // KV tiles of this split, clipped by the masks at tile granularity (as kv_tile_range
     // of the tiled kernel, for the single query row at position q_pos0)
@@ -162,8 +163,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
                 const uint32_t ph = (slot / kDStages) & 1;
                 if (!mbar_wait(bar_empty + 8 * st, ph ^ 1, abort_flag)) return false;
                 mbar_expect_tx(bar_full + 8 * st, kDTileBytes);
-                tma_load_3d(sRing + st * kDTileBytes, map, bar_full + 8 * st, 0, tile * kTile, unit);
-                tma_load_3d(sRing + st * kDTileBytes + kTile * 128, map, bar_full + 8 * st, 64, tile * kTile, unit);
+                tma_load_3d(sRing + st * kDTileBytes, map, bar_full + 8 * st, 0, tile * kTile, kv_unit);
+                tma_load_3d(sRing + st * kDTileBytes + kTile * 128, map, bar_full + 8 * st, 64, tile * kTile, kv_unit);
                 ++slot;
                 return true;
             };

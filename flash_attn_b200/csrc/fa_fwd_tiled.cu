@@ -296,6 +296,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int rem = blockIdx.x - unit0 * per_unit;
     const int unit = unit0 + rem % gsize;
     const int bx = rem / gsize;
+    const int kv_unit = a.kv_group > 1 ? unit / a.kv_group : unit;  // grouped-query attention: K/V head of this unit
     const int split = bx % a.num_splits;
     int qb = bx / a.num_splits;
     if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
@@ -356,11 +357,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
 #pragma unroll
                 for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, unit);
+                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, kv_unit);
                 mbar_expect_tx(bar_v_full + 8 * t, C::kTileBytes);
 #pragma unroll
                 for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, unit);
+                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, kv_unit);
             }
         }
     }
@@ -394,13 +395,13 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
 #pragma unroll
                     for (int b = 0; b < C::kBoxes; ++b)
-                        tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, unit);
+                        tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, kv_unit);
                     if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
                     FA_TR(11);
                     mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
 #pragma unroll
                     for (int b = 0; b < C::kBoxes; ++b)
-                        tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, unit);
+                        tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, kv_unit);
                 }
             }
         } else if (n_union > 0 && warp == C::kMmaWarp) {

@@ -21,6 +21,7 @@ struct FwdArgs {
     int heads;
     int units;              // batch * heads of this launch
     int unit_group;         // units whose CTAs are interleaved in launch order (1 = unit-major)
+    int kv_group;           // query units per K/V unit (grouped-query attention); K/V unit = unit / kv_group
     int seqlen_q, seqlen_k, head_dim;
     int tr, tc;             // query / key tiles
     int num_splits, tiles_per_split;
@@ -47,6 +48,7 @@ struct DecodeArgs {
     const float* alibi_slopes;
     int* status;
     int heads;
+    int kv_group;           // query units per K/V unit; K/V unit = unit / kv_group
     int seqlen_k, head_dim;
     int tc;
     int num_splits, tiles_per_split;

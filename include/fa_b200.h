@@ -80,6 +80,10 @@ typedef struct fa_fwd_params {
     size_t workspace_bytes;
     int* status;              /* device int or NULL: set non-zero if a device wait timed out */
     void* stream;             /* cudaStream_t; NULL = default stream (the reference's)       */
+    int heads_k;              /* K/V heads for grouped-query attention: K and V are
+                                 [batch, heads_k, seqlen_k, head_dim], heads % heads_k == 0 and
+                                 query head h reads K/V head h / (heads / heads_k).  0 = heads
+                                 (the reference has one head count, gridDim.y, main.cu:142) */
 } fa_fwd_params;
 
 /* Forward pass: O = dropout(softmax(scale*Q K^T - slope*|i-j| + masks)) V, LSE.

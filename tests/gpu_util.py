@@ -20,17 +20,33 @@ def to_dev(x, dtype_name):
 
 def run_case(B, H, Nq, Nk, d, dtype="bfloat16", seed=0, sigma=1.0, scale=None, causal=False, window=(-1, -1),
              alibi=False, p_dropout=0.0, drop_seed=42, offset=0, num_splits=1, q_pos0=0, k_pos0=0,
-             out_dtype=None, rows=None):
-    """Returns dict with errors of the CUDA result against the oracle."""
+             out_dtype=None, rows=None, heads_k=None, host=False):
+    """Returns dict with errors of the CUDA result against the oracle.  heads_k < H runs
+    grouped-query attention (the oracle sees K/V repeated per query head); host=True goes
+    through the host-buffer entry point."""
     import flash_attn_b200 as fa
     q, k, v = synth.qkv(seed, B, H, Nq, Nk, d, dtype, sigma)
+    k_dev, v_dev = k, v
+    if heads_k is not None and heads_k != H:
+        k_dev = np.ascontiguousarray(k[:, :heads_k])
+        v_dev = np.ascontiguousarray(v[:, :heads_k])
+        k = np.repeat(k_dev, H // heads_k, axis=1)
+        v = np.repeat(v_dev, H // heads_k, axis=1)
     slopes = synth.alibi_slopes(H) if alibi else None
     scale = float(scale if scale is not None else 1.0 / np.sqrt(d))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    o, lse = fa.flash_attn_forward(
-        to_dev(q, dtype), to_dev(k, dtype), to_dev(v, dtype), softmax_scale=scale, causal=causal, window=window,
-        alibi_slopes=None if slopes is None else torch.from_numpy(slopes), p_dropout=p_dropout, seed=drop_seed,
-        offset=offset, num_splits=num_splits, q_pos0=q_pos0, k_pos0=k_pos0, out_dtype=out_dtype, status=status)
+    if host:
+        pin = lambda x: torch.from_numpy(x).to(TORCH_DT[dtype]).pin_memory()
+        o, lse = fa.flash_attn_forward_host(
+            pin(q), pin(k_dev), pin(v_dev), softmax_scale=scale, causal=causal, window=window,
+            alibi_slopes=None if slopes is None else torch.from_numpy(slopes), p_dropout=p_dropout, seed=drop_seed,
+            offset=offset, num_splits=num_splits, out_dtype=out_dtype)
+    else:
+        o, lse = fa.flash_attn_forward(
+            to_dev(q, dtype), to_dev(k_dev, dtype), to_dev(v_dev, dtype), softmax_scale=scale, causal=causal,
+            window=window, alibi_slopes=None if slopes is None else torch.from_numpy(slopes), p_dropout=p_dropout,
+            seed=drop_seed, offset=offset, num_splits=num_splits, q_pos0=q_pos0, k_pos0=k_pos0, out_dtype=out_dtype,
+            status=status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, f"device wait timed out: status {int(status.item())}"
     # the split count the library really used decides the dropout stream geometry

@@ -96,6 +96,12 @@ def test_error_paths_without_a_gpu(lib):
     assert lib.fa_fwd_workspace_bytes(ctypes.byref(p)) == ((4 * 128 * 64 * 4 + 255) // 256 + (4 * 128 * 4 + 255) // 256) * 256
     p.num_splits = 100                                  # clamped to the number of KV tiles
     assert lib.fa_fwd_resolve_splits(ctypes.byref(p)) == 8
+    p.heads, p.heads_k = 6, 4                           # query heads must be a multiple of K/V heads
+    assert lib.fa_fwd_resolve_splits(ctypes.byref(p)) == -1
+    p.heads_k = 3
+    assert lib.fa_fwd_resolve_splits(ctypes.byref(p)) == 8
+    p.head_dim, p.num_splits = 60, 1                    # padded copy: Q and O for 6 heads, K and V for 3
+    assert lib.fa_fwd_workspace_bytes(ctypes.byref(p)) == 2 * 6 * 128 * 64 * 2 + 2 * 3 * 1024 * 64 * 2
     for code in range(-7, 1):
         assert lib.fa_strerror(code)
     assert _lib.strerror(-3).startswith("workspace")
