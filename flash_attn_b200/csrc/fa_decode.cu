@@ -15,8 +15,15 @@
 // The MMAs are tiny (N = 16): the tensor pipe is a convenient dot-product engine that
 // reads K/V straight from the swizzled TMA tiles, and the kernel stays HBM-bound.
 //
+// Grouped-query attention (kH = 8): the query heads that share one K/V head ride in columns
+// 0..7 of the same MMAs (rows 0..7 of the Q and P operand tiles), so a CTA streams its K/V
+// split once for up to eight heads; every per-query quantity (max, sum, ALiBi slope, dropout
+// stream, LSE) becomes an array over the heads.  Groups larger than eight are cut into
+// sub-groups of eight heads, one CTA each.
+//
 // Stream order of the TMA ring: K(0), K(1), V(0), K(2), V(1), ... (chunks of four tiles), so
 // the scores of chunk c+1 are computed while the softmax of chunk c runs.
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "fa_internal.h"
@@ -36,8 +43,8 @@ constexpr int kDSmemP = kDStages * kDTileBytes;                  // 8 KB + 2 KB 
 constexpr int kDSmemQ = kDSmemP + kChunkTiles * kPTileBytes + 2048;  // 2 KB + 2 KB slack
 constexpr int kDSmemBar = kDSmemQ + 4096;
 constexpr int kDNumBars = 2 * kDStages + 2 + 2 + 3;
-constexpr int kDSmemRed = kDSmemBar + 8 * kDNumBars;             // float[2][4] + float[4]
-constexpr int kDSmemMisc = kDSmemRed + 64;
+constexpr int kDSmemRed = kDSmemBar + 8 * kDNumBars;             // float[2][4][8] maxima + float[4][8] sums
+constexpr int kDSmemMisc = kDSmemRed + 384;
 constexpr int kDSmemBytes = kDSmemMisc + 16 + 1024;
 constexpr int kDTmemCols = 256;            // S^T: 2 buffers x 4 tiles x 16 columns; O^T: 16 columns at 128
 
@@ -63,12 +70,33 @@ __device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
 __device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(v) : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+// kH columns of one TMEM lane (kH = 1 or 8)
+template <int kH>
+__device__ __forceinline__ void tmem_ld_heads(uint32_t taddr, uint32_t (&r)[kH]) {
+    if constexpr (kH == 1) r[0] = tmem_ld1(taddr);
+    else tmem_ld8(taddr, r);
+}
+template <int kH>
+__device__ __forceinline__ void tmem_st_heads(uint32_t taddr, const uint32_t (&r)[kH]) {
+    if constexpr (kH == 1) tmem_st1(taddr, r[0]);
+    else tmem_st8(taddr, r);
+}
 __device__ __forceinline__ bool mbar_wait_warp_ok(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag) ? 1 : 0) != 0;
 }
 __device__ __forceinline__ void named_barrier_128() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
-template <bool kBf16>
+template <bool kBf16, int kH>
 __global__ void __launch_bounds__(kDThreads, 2)
 decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v, const DecodeArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -91,9 +119,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int unit = blockIdx.x / a.num_splits;
-    const int split = blockIdx.x - unit * a.num_splits;
-    const int kv_unit = a.kv_group > 1 ? unit / a.kv_group : unit;  // grouped-query attention: K/V head of this unit
+    // kH = 1: one CTA per (query unit, split).  kH = 8: one CTA per (K/V unit, sub-group of up to
+    // eight of its query heads, split); `unit` is then the first query unit of the sub-group.
+    const int cta_unit = blockIdx.x / a.num_splits;
+    const int split = blockIdx.x - cta_unit * a.num_splits;
+    int unit, kv_unit, gh = 1;
+    if constexpr (kH == 1) {
+        unit = cta_unit;
+        kv_unit = a.kv_group > 1 ? unit / a.kv_group : unit;
+    } else {
+        kv_unit = cta_unit / a.subgroups;
+        const int sub = cta_unit - kv_unit * a.subgroups;
+        unit = kv_unit * a.kv_group + sub * kH;
+        gh = min(kH, a.kv_group - sub * kH);  // query heads of this CTA
+    }
 
     // KV tiles of this split, clipped by the masks at tile granularity (as kv_tile_range
     // of the tiled kernel, for the single query row at position q_pos0)
@@ -133,13 +172,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kDTmemCols);
         tmem_relinquish();
     }
-    if (threadIdx.x < 16 && n_tiles > 0) {
-        // the query row goes to row 0 of the two Q atoms (16-byte unit u -> atom u/8, unit u%8)
-        const int u = threadIdx.x;
+    if (threadIdx.x < 16 * kH && n_tiles > 0) {
+        // query head n goes to row n of the two Q atoms (16-byte unit u -> atom u/8, unit (u%8) ^ n:
+        // the 128-byte swizzle of row n)
+        const int u = threadIdx.x & 15, n = threadIdx.x >> 4;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (u * 8 < a.head_dim)
-            val = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.q) + static_cast<long long>(unit) * a.head_dim + u * 8);
-        *reinterpret_cast<uint4*>(smem_gen + kDSmemQ + (u >> 3) * 1024 + (u & 7) * 16) = val;
+        if (n < gh && u * 8 < a.head_dim)
+            val = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.q) + static_cast<long long>(unit + n) * a.head_dim + u * 8);
+        *reinterpret_cast<uint4*>(smem_gen + kDSmemQ + (u >> 3) * 1024 + n * 128 + (((u & 7) ^ n) << 4)) = val;
         fence_proxy_async_smem();
     }
     if (warp == 4 && lane == 0) {
@@ -242,13 +282,18 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         const int r = threadIdx.x;  // key inside a tile; output column in the epilogue
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         const float scale2 = a.scale_log2;
-        float slope2 = 0.0f;
-        if (a.alibi_slopes != nullptr) slope2 = a.alibi_slopes[unit % a.heads] * kDLog2e;
+        float slope2[kH];
+#pragma unroll
+        for (int n = 0; n < kH; ++n)
+            slope2[n] = (a.alibi_slopes != nullptr && n < gh) ? a.alibi_slopes[(unit + n) % a.heads] * kDLog2e : 0.0f;
         const bool dropout = a.drop.threshold != 0ull;
-        const unsigned long long subseq =
-            (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.num_splits) + static_cast<unsigned long long>(split);
-        float m_ref = -INFINITY;  // CTA-wide running max, log2 units
-        float l_part = 0.0f;      // this thread's share of the row sum
+        float m_ref[kH];   // CTA-wide running max per head, log2 units
+        float l_part[kH];  // this thread's share of each head's row sum
+#pragma unroll
+        for (int n = 0; n < kH; ++n) {
+            m_ref[n] = -INFINITY;
+            l_part[n] = 0.0f;
+        }
 
         for (int c = 0; c < n_chunks; ++c) {
             const int buf = c & 1;
@@ -256,19 +301,24 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
             bool ok = mbar_wait_warp_ok(bar_s_full + 8 * buf, (c >> 1) & 1, abort_flag);
             if (!ok) fail = 3;
             tc_fence_after_sync();
-            float v[kChunkTiles];
+            float v[kChunkTiles][kH];
 #pragma unroll
             for (int t = 0; t < kChunkTiles; ++t) {
-                uint32_t raw = 0;
-                if (t < nt) raw = tmem_ld1(tmem_base + lane_base + buf * 64 + t * 16);
-                v[t] = __uint_as_float(raw);
+                uint32_t raw[kH];
+#pragma unroll
+                for (int n = 0; n < kH; ++n) raw[n] = 0u;
+                if (t < nt) tmem_ld_heads<kH>(tmem_base + lane_base + buf * 64 + t * 16, raw);
+#pragma unroll
+                for (int n = 0; n < kH; ++n) v[t][n] = __uint_as_float(raw[n]);
             }
             tmem_wait_ld();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_s_free + 8 * buf);
 
-            float m_thr = -INFINITY;
+            float m_thr[kH];
+#pragma unroll
+            for (int n = 0; n < kH; ++n) m_thr[n] = -INFINITY;
 #pragma unroll
             for (int t = 0; t < kChunkTiles; ++t) {
                 const int tile = lo + c * kChunkTiles + t;
@@ -278,55 +328,83 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
                 if (a.is_causal && kpos > a.q_pos0) keep = false;
                 if (a.window_left >= 0 && a.q_pos0 - kpos > a.window_left) keep = false;
                 if (a.window_right >= 0 && kpos - a.q_pos0 > a.window_right) keep = false;
-                float s = v[t] * scale2;
-                if (slope2 != 0.0f) s = fmaf(-slope2, fabsf(static_cast<float>(a.q_pos0 - kpos)), s);
-                v[t] = keep ? s : -INFINITY;
-                m_thr = fmaxf(m_thr, v[t]);
+                const float dist = fabsf(static_cast<float>(a.q_pos0 - kpos));
+#pragma unroll
+                for (int n = 0; n < kH; ++n) {
+                    float sc = v[t][n] * scale2;
+                    if (slope2[n] != 0.0f) sc = fmaf(-slope2[n], dist, sc);
+                    v[t][n] = keep ? sc : -INFINITY;
+                    m_thr[n] = fmaxf(m_thr[n], v[t][n]);
+                }
             }
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) m_thr = fmaxf(m_thr, __shfl_xor_sync(0xffffffffu, m_thr, o));
-            if (lane == 0) red[buf * 4 + warp] = m_thr;
+            for (int n = 0; n < kH; ++n) {
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) m_thr[n] = fmaxf(m_thr[n], __shfl_xor_sync(0xffffffffu, m_thr[n], o));
+                if (lane == 0) red[(buf * 4 + warp) * 8 + n] = m_thr[n];
+            }
             named_barrier_128();
-            const float m_chunk = fmaxf(fmaxf(red[buf * 4], red[buf * 4 + 1]), fmaxf(red[buf * 4 + 2], red[buf * 4 + 3]));
 
             // the previous chunk's P V must be done before P is overwritten or O rescaled
             if (c > 0) {
                 if (!mbar_wait_warp_ok(bar_p_free, (c - 1) & 1, abort_flag)) fail = 4;
                 tc_fence_after_sync();
             }
-            float m_new = m_ref, factor = 1.0f;
-            if (m_chunk > m_ref + 8.0f || m_ref == -INFINITY) {
-                m_new = fmaxf(m_ref, m_chunk);
-                factor = (m_ref == -INFINITY) ? 0.0f : ex2f(m_ref - m_new);
+            float m_use[kH], factor[kH];
+            bool any_rescale = false;
+#pragma unroll
+            for (int n = 0; n < kH; ++n) {
+                const float m_chunk = fmaxf(fmaxf(red[(buf * 4) * 8 + n], red[(buf * 4 + 1) * 8 + n]),
+                                            fmaxf(red[(buf * 4 + 2) * 8 + n], red[(buf * 4 + 3) * 8 + n]));
+                float m_new = m_ref[n];
+                factor[n] = 1.0f;
+                if (m_chunk > m_ref[n] + 8.0f || m_ref[n] == -INFINITY) {
+                    m_new = fmaxf(m_ref[n], m_chunk);
+                    factor[n] = (m_ref[n] == -INFINITY) ? 0.0f : ex2f(m_ref[n] - m_new);
+                }
+                if (m_new != m_ref[n]) {
+                    any_rescale = true;
+                    l_part[n] *= factor[n];
+                }
+                m_ref[n] = m_new;
+                m_use[n] = (m_new == -INFINITY) ? 0.0f : m_new;
             }
-            if (c > 0 && m_new != m_ref) {  // CTA-uniform: every thread sees the same maxima
-                const uint32_t ov = tmem_ld1(tmem_o + lane_base);
+            if (c > 0 && any_rescale) {  // CTA-uniform: every thread sees the same maxima
+                uint32_t ov[kH];
+                tmem_ld_heads<kH>(tmem_o + lane_base, ov);
                 tmem_wait_ld();
-                tmem_st1(tmem_o + lane_base, __float_as_uint(__uint_as_float(ov) * factor));
+#pragma unroll
+                for (int n = 0; n < kH; ++n) ov[n] = __float_as_uint(__uint_as_float(ov[n]) * factor[n]);
+                tmem_st_heads<kH>(tmem_o + lane_base, ov);
                 tmem_wait_st();
             }
-            if (m_new != m_ref) l_part *= factor;
-            m_ref = m_new;
-            const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
 
 #pragma unroll
             for (int t = 0; t < kChunkTiles; ++t) {
                 if (t < nt) {
-                    const float p = ex2f(v[t] - m_use);
-                    l_part += p;
-                    bool kept = true;
-                    if (dropout) {
-                        // reference draw order for query row 0: draw 64*tile_index + 8*(col/16) + 2*((col%16)/8) + col%2
-                        const unsigned long long first = 64ull * static_cast<unsigned long long>(c * kChunkTiles + t) +
-                                                         8ull * (r >> 4);
-                        const uint32_t bits = philox_keep4(a.drop, subseq, first);
-                        kept = (bits >> (2 * ((r >> 3) & 1) + (r & 1))) & 1u;
+#pragma unroll
+                    for (int n = 0; n < kH; ++n) {
+                        const float p = ex2f(v[t][n] - m_use[n]);
+                        l_part[n] += p;
+                        bool kept = true;
+                        if (dropout && n < gh) {
+                            // reference draw order for query row 0: draw 64*tile_index + 8*(col/16) + 2*((col%16)/8) + col%2
+                            const unsigned long long subseq =
+                                (a.drop.unit0 + unit + n) * static_cast<unsigned long long>(a.num_splits) +
+                                static_cast<unsigned long long>(split);
+                            const unsigned long long first = 64ull * static_cast<unsigned long long>(c * kChunkTiles + t) +
+                                                             8ull * (r >> 4);
+                            const uint32_t bits = philox_keep4(a.drop, subseq, first);
+                            kept = (bits >> (2 * ((r >> 3) & 1) + (r & 1))) & 1u;
+                        }
+                        const float pk = kept ? p : 0.0f;
+                        uint16_t h;
+                        if constexpr (kBf16) h = __bfloat16_as_ushort(__float2bfloat16_rn(pk));
+                        else h = __half_as_ushort(__float2half_rn(pk));
+                        // P operand row n (head n), 128-byte swizzled like the Q rows
+                        *reinterpret_cast<uint16_t*>(smem_gen + kDSmemP + t * kPTileBytes + (r >> 6) * 1024 + n * 128 +
+                                                     (((((r & 63) >> 3) ^ n) & 7) << 4) + (r & 7) * 2) = h;
                     }
-                    const float pk = kept ? p : 0.0f;
-                    uint16_t h;
-                    if constexpr (kBf16) h = __bfloat16_as_ushort(__float2bfloat16_rn(pk));
-                    else h = __half_as_ushort(__float2half_rn(pk));
-                    *reinterpret_cast<uint16_t*>(smem_gen + kDSmemP + t * kPTileBytes + (r >> 6) * 1024 + (r & 63) * 2) = h;
                 }
             }
             fence_proxy_async_smem();
@@ -336,35 +414,44 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         }
 
         // ---- epilogue ----------------------------------------------------------------
-        float l_warp = l_part;
 #pragma unroll
-        for (int o = 16; o >= 1; o >>= 1) l_warp += __shfl_xor_sync(0xffffffffu, l_warp, o);
-        if (lane == 0) red[8 + warp] = l_warp;
+        for (int n = 0; n < kH; ++n) {
+            float l_warp = l_part[n];
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) l_warp += __shfl_xor_sync(0xffffffffu, l_warp, o);
+            if (lane == 0) red[64 + warp * 8 + n] = l_warp;
+        }
         named_barrier_128();
-        const float l_sum = (red[8] + red[9]) + (red[10] + red[11]);
-        float o_val = 0.0f;
+        uint32_t o_raw[kH];
+#pragma unroll
+        for (int n = 0; n < kH; ++n) o_raw[n] = 0u;
         if (n_tiles > 0 && fail == 0) {
             if (mbar_wait_warp_ok(bar_o_done, 0, abort_flag)) {
                 tc_fence_after_sync();
-                o_val = __uint_as_float(tmem_ld1(tmem_o + lane_base));
+                tmem_ld_heads<kH>(tmem_o + lane_base, o_raw);
                 tmem_wait_ld();
             } else {
                 fail = 5;
             }
         }
-        const float inv = l_sum > 0.0f ? a.drop.inv_keep / l_sum : 0.0f;
-        const float lse_val = l_sum > 0.0f ? m_ref * kDLn2 + __logf(l_sum) : -INFINITY;
-        o_val *= inv;
-        const long long out_row = (a.num_splits > 1) ? static_cast<long long>(unit) * a.num_splits + split : unit;
-        if (r < a.head_dim) {
-            if (a.num_splits > 1) a.o_partial[out_row * a.head_dim + r] = o_val;
-            else if (a.o_is_fp32) static_cast<float*>(a.o)[out_row * a.head_dim + r] = o_val;
-            else if (kBf16) static_cast<__nv_bfloat16*>(a.o)[out_row * a.head_dim + r] = __float2bfloat16_rn(o_val);
-            else static_cast<__half*>(a.o)[out_row * a.head_dim + r] = __float2half_rn(o_val);
-        }
-        if (r == 0) {
-            if (a.num_splits > 1) a.lse_partial[out_row] = lse_val;
-            else if (a.lse != nullptr) a.lse[out_row] = lse_val;
+#pragma unroll
+        for (int n = 0; n < kH; ++n) {
+            if (n >= gh) continue;
+            const float l_sum = (red[64 + n] + red[64 + 8 + n]) + (red[64 + 16 + n] + red[64 + 24 + n]);
+            const float inv = l_sum > 0.0f ? a.drop.inv_keep / l_sum : 0.0f;
+            const float lse_val = l_sum > 0.0f ? m_ref[n] * kDLn2 + __logf(l_sum) : -INFINITY;
+            const float o_val = __uint_as_float(o_raw[n]) * inv;
+            const long long out_row = (a.num_splits > 1) ? static_cast<long long>(unit + n) * a.num_splits + split : unit + n;
+            if (r < a.head_dim) {
+                if (a.num_splits > 1) a.o_partial[out_row * a.head_dim + r] = o_val;
+                else if (a.o_is_fp32) static_cast<float*>(a.o)[out_row * a.head_dim + r] = o_val;
+                else if (kBf16) static_cast<__nv_bfloat16*>(a.o)[out_row * a.head_dim + r] = __float2bfloat16_rn(o_val);
+                else static_cast<__half*>(a.o)[out_row * a.head_dim + r] = __float2half_rn(o_val);
+            }
+            if (r == 0) {
+                if (a.num_splits > 1) a.lse_partial[out_row] = lse_val;
+                else if (a.lse != nullptr) a.lse[out_row] = lse_val;
+            }
         }
     }
 
@@ -385,13 +472,20 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
 }  // namespace
 
-cudaError_t launch_decode(const DecodeArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, int units, bool bf16,
+cudaError_t launch_decode(const DecodeArgs& a_in, const CUtensorMap& tk, const CUtensorMap& tv, int units, bool bf16,
                           cudaStream_t stream) {
-    static bool configured[2][64] = {};
+    static bool configured[4][64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    const long long ctas = static_cast<long long>(units) * a.num_splits;
+    DecodeArgs a = a_in;
+    // query heads that share a K/V head are packed into one CTA, eight at a time
+    // (development switch: FA_B200_DECODE_PACK=0 keeps one CTA per query head)
+    static const bool allow_pack = [] { const char* e = std::getenv("FA_B200_DECODE_PACK"); return !(e && e[0] == '0'); }();
+    const bool packed = a.kv_group > 1 && allow_pack;
+    a.subgroups = packed ? (a.kv_group + 7) / 8 : 1;
+    const long long cta_units = packed ? static_cast<long long>(units / a.kv_group) * a.subgroups : units;
+    const long long ctas = cta_units * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     auto run = [&](auto kern, int which) -> cudaError_t {
         if (dev < 0 || dev >= 64 || !configured[which][dev]) {
@@ -402,7 +496,8 @@ cudaError_t launch_decode(const DecodeArgs& a, const CUtensorMap& tk, const CUte
         kern<<<static_cast<unsigned>(ctas), kDThreads, kDSmemBytes, stream>>>(tk, tv, a);
         return cudaGetLastError();
     };
-    return bf16 ? run(decode_kernel<true>, 0) : run(decode_kernel<false>, 1);
+    if (packed) return bf16 ? run(decode_kernel<true, 8>, 2) : run(decode_kernel<false, 8>, 3);
+    return bf16 ? run(decode_kernel<true, 1>, 0) : run(decode_kernel<false, 1>, 1);
 }
 
 }  // namespace fa

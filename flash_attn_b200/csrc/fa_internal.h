@@ -49,6 +49,7 @@ struct DecodeArgs {
     int* status;
     int heads;
     int kv_group;           // query units per K/V unit; K/V unit = unit / kv_group
+    int subgroups;          // CTAs (of up to eight query heads) per K/V unit when kv_group > 1; set by launch_decode
     int seqlen_k, head_dim;
     int tc;
     int num_splits, tiles_per_split;

@@ -33,6 +33,19 @@ def test_gqa_decode(Hk, splits):
     gpu_util.assert_close(res, f"gqa decode Hk={Hk} splits={splits}")
 
 
+@pytest.mark.parametrize("H,Hk", [(16, 1), (6, 2), (24, 2)])
+def test_gqa_decode_group_sizes(H, Hk):
+    # groups of 16 and 12 heads are cut into sub-groups of eight; a group of 3 leaves operand rows unused
+    res = gpu_util.run_case(1, H, 1, 2100, 128, heads_k=Hk, num_splits=3, seed=17)
+    gpu_util.assert_close(res, f"gqa decode H={H} Hk={Hk}")
+
+
+def test_gqa_decode_dropout_alibi_window_fp16():
+    res = gpu_util.run_case(2, 8, 1, 1000, 64, dtype="float16", heads_k=2, num_splits=2, q_pos0=999, causal=True,
+                            window=(600, 0), alibi=True, p_dropout=0.2, seed=18)
+    gpu_util.assert_close(res, "gqa decode dropout alibi window")
+
+
 def test_gqa_host_buffers():
     res = gpu_util.run_case(3, 6, 256, 256, 128, causal=True, heads_k=2, host=True, seed=16)
     gpu_util.assert_close(res, "gqa host path")
