@@ -41,6 +41,10 @@ WORKLOADS = {
                     "NCCL send/recv, LSE merge)"),
     "c4": dict(B=64, H=32, Nq=1, Nk=32768, d=128, causal=False, window=(-1, -1), alibi=False, p=0.0, splits=16,
                desc="config 4: split-KV decode bf16 B=64 H=32 q=1 kv=32768 d=128, 16 splits + LSE combine"),
+    # config 4 with grouped-query attention (not a baseline config: the reference has one head count)
+    "c4gqa": dict(B=64, H=32, Hk=8, Nq=1, Nk=32768, d=128, causal=False, window=(-1, -1), alibi=False, p=0.0,
+                  splits=16, desc="config 4 with 8 K/V heads for the 32 query heads (grouped-query decode): bf16 B=64 "
+                                  "q=1 kv=32768 d=128, 16 splits + LSE combine"),
 }
 
 
@@ -68,7 +72,8 @@ def work_per_step(name, w):
         flops = 4.0 * units * w["Nq"] * w["Nk"] * w["d"] / 2  # causal convention 4*B*H*N^2*d/2
     else:
         flops = 4.0 * units * attended_pairs(w) * w["d"]
-    nbytes = 2.0 * units * w["d"] * (2 * w["Nk"] + 2 * w["Nq"])  # K + V + Q + O, 16-bit
+    kv_units = w["B"] * w.get("Hk", w["H"])
+    nbytes = 2.0 * w["d"] * (2 * kv_units * w["Nk"] + 2 * units * w["Nq"])  # K + V + Q + O, 16-bit
     return flops, nbytes
 
 
@@ -232,8 +237,9 @@ def make_inputs(torch, w, seed, device, copies):
     sets = []
     for _ in range(copies):
         q = torch.randn((w["B"], w["H"], w["Nq"], w["d"]), generator=g, device=device, dtype=torch.float32).bfloat16()
-        k = torch.randn((w["B"], w["H"], w["Nk"], w["d"]), generator=g, device=device, dtype=torch.float32).bfloat16()
-        v = torch.randn((w["B"], w["H"], w["Nk"], w["d"]), generator=g, device=device, dtype=torch.float32).bfloat16()
+        hk = w.get("Hk", w["H"])
+        k = torch.randn((w["B"], hk, w["Nk"], w["d"]), generator=g, device=device, dtype=torch.float32).bfloat16()
+        v = torch.randn((w["B"], hk, w["Nk"], w["d"]), generator=g, device=device, dtype=torch.float32).bfloat16()
         sets.append((q, k, v))
     return sets
 
@@ -282,7 +288,7 @@ def time_e2e(torch, fa, w, steps, warmup, rank):
     g = torch.Generator()
     g.manual_seed(1234 + rank)
     shape_q = (w["B"], w["H"], w["Nq"], w["d"])
-    shape_k = (w["B"], w["H"], w["Nk"], w["d"])
+    shape_k = (w["B"], w.get("Hk", w["H"]), w["Nk"], w["d"])
     q = torch.randn(shape_q, generator=g).bfloat16().pin_memory()
     k = torch.randn(shape_k, generator=g).bfloat16().pin_memory()
     v = torch.randn(shape_k, generator=g).bfloat16().pin_memory()
@@ -311,18 +317,25 @@ def time_e2e(torch, fa, w, steps, warmup, rank):
 def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks):
     """Config 5: ONE problem sharded over the ranks (strong scaling): each rank holds two zig-zag
     chunks of the sequence; K/V chunks go round the ring while the forward kernel works."""
-    from flash_attn_b200 import ring
+    from flash_attn_b200 import ring, ulysses
+    use_a2a = args.seq_parallel == "ulysses"
     N, C = w["Nq"], w["Nq"] // (2 * world)
     g = torch.Generator(device=dev)
     g.manual_seed(5 + rank)
-    mk = lambda: [(0.5 * torch.randn((w["B"], w["H"], C, w["d"]), generator=g, device=dev)).bfloat16() for _ in range(2)]
+    if use_a2a:
+        # contiguous slice of 2*C rows per rank; two all-to-alls trade it for whole sequences of H/P heads
+        mk = lambda: (0.5 * torch.randn((w["B"], w["H"], 2 * C, w["d"]), generator=g, device=dev)).bfloat16()
+        run_step = lambda: ulysses.ulysses_attention_forward(q, k, v, causal=True)
+    else:
+        mk = lambda: [(0.5 * torch.randn((w["B"], w["H"], C, w["d"]), generator=g, device=dev)).bfloat16() for _ in range(2)]
+        run_step = lambda: ring.ring_attention_forward(q, k, v, causal=True)
     q, k, v = mk(), mk(), mk()
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
     if sampler:
         sampler.start()
         sampler.wait_first_sample()
     for _ in range(args.warmup):
-        ring.ring_attention_forward(q, k, v, causal=True)
+        run_step()
     barrier()
     torch.cuda.synchronize()
     if sampler:
@@ -330,7 +343,7 @@ def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        ring.ring_attention_forward(q, k, v, causal=True)
+        run_step()
     e1.record()
     torch.cuda.synchronize()
     barrier()
@@ -344,13 +357,18 @@ def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, 
         "metric": "fwd_attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": w["desc"], "chunk_rows": C, "kv_bytes_per_ring_step_per_rank": 4 * w["B"] * w["H"] * C * w["d"] * 2,
-                   "l2": "each rank streams 2 x %d MB of K/V per ring step (> L2)" % (2 * w["H"] * C * w["d"] * 2 // 2 ** 20),
-                   "flops_per_step_total": flops},
+        "config": ({"workload": w["desc"].replace("sequence ring over the ranks (zig-zag chunks, NCCL send/recv, LSE merge)",
+                                                   "head all-to-all over the ranks (NCCL), whole sequences of H/P heads per rank"),
+                    "rows_per_rank": 2 * C, "a2a_bytes_sent_per_rank": (4 * w["B"] * w["H"] * 2 * C * w["d"] * 2) * (world - 1) // world,
+                    "l2": "each rank reads %d MB of K/V per step (> L2)" % (2 * w["B"] * w["H"] // world * N * w["d"] * 2 // 2 ** 20),
+                    "flops_per_step_total": flops} if use_a2a else
+                   {"workload": w["desc"], "chunk_rows": C, "kv_bytes_per_ring_step_per_rank": 4 * w["B"] * w["H"] * C * w["d"] * 2,
+                    "l2": "each rank streams 2 x %d MB of K/V per ring step (> L2)" % (2 * w["H"] * C * w["d"] * 2 // 2 ** 20),
+                    "flops_per_step_total": flops}),
         "clocks": clocks,
         "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "note": "the ring works on device-resident shards; the host-buffer path is measured on config 2"},
-        "gpu_launches": (2 * pairs + 2) * args.steps * world,
+        "gpu_launches": (1 if use_a2a else 2 * pairs + 2) * args.steps * world,
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tensor_sustained"] or peaks["tensor"],
                      "unit": "TFLOP/s", "frac": value / world / (peaks["tensor_sustained"] or peaks["tensor"]),
                      "peak_source": peaks["source"] + " sustained (seconds-long step)", "traffic": None,
@@ -371,6 +389,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--seq-parallel", default="ring", choices=["ring", "ulysses"],
+                    help="config 5: K/V ring with LSE merge (default) or head all-to-all")
     ap.add_argument("--no-secondary", action="store_true", help="skip the c3/c4 side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
@@ -378,7 +398,7 @@ def main():
                     "for profiler captures; the JSON line then describes the reduced workload)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"c2": 2000, "c3": 200, "c4": 50, "c5": 5}[args.workload] if args.impl == "ours" else 2
+        args.steps = {"c2": 2000, "c3": 200, "c4": 50, "c4gqa": 100, "c5": 5}[args.workload] if args.impl == "ours" else 2
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
@@ -424,7 +444,7 @@ def main():
     if name == "c5":
         return run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks)
     # two input sets (2 x 268 MB for config 2) alternate, so no step finds its inputs in the 126 MB L2
-    sets = make_inputs(torch, w, 2 + rank, dev, copies=2 if name != "c4" else 1)
+    sets = make_inputs(torch, w, 2 + rank, dev, copies=2 if not name.startswith("c4") else 1)
 
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
     if sampler:
@@ -442,7 +462,7 @@ def main():
         e2e_sec, h2d, d2h = time_e2e(torch, fa, w, max(3, min(args.steps, 10)), 2, rank)
         e2e_sec = max_over_ranks(e2e_sec)
 
-    is_decode = name == "c4"
+    is_decode = name.startswith("c4")
     if is_decode:
         metric, unit = "decode_hbm_gbs", "GB/s"
         value = world * nbytes / sec / 1e9
@@ -458,7 +478,7 @@ def main():
     # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
     # summarised under profiles/: config 2 captured at full size, config 4 captured on 128 of the
     # 2048 units and scaled by the units processed; null where no capture of the workload exists
-    ncu_traffic = {"c2": 201.42e6 + 47.13e6, "c4": 16 * (2.1476e9 + 5.1e6)}
+    ncu_traffic = {"c2": 201.42e6 + 47.13e6, "c4": 16 * (2.1476e9 + 5.1e6)}  # no capture of c3 / c4gqa
     roof["traffic"] = ncu_traffic.get(name) if args.batch is None else None
     roof["traffic_source"] = "ncu capture (static figure, not measured in this run)" if roof["traffic"] else None
     roof["kernel"] = "decode_kernel (+ combine_kernel)" if is_decode else "fwd_tiled_kernel"
@@ -469,7 +489,7 @@ def main():
         "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["desc"], "units_per_gpu": w["B"] * w["H"], "l2": "two input sets alternate; each "
-                   "step reads inputs larger than the 126 MB L2" if name != "c4" else "34 GB streamed per step",
+                   "step reads inputs larger than the 126 MB L2" if not is_decode else "%.1f GB streamed per step" % (nbytes / 1e9),
                    "flops_per_step_per_gpu": flops, "bytes_per_step_per_gpu": nbytes},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -480,13 +500,13 @@ def main():
 
     if rank == 0 and world == 1 and not args.no_secondary and name == "c2":
         side = {}
-        for other in ("c3", "c4"):
+        for other in ("c3", "c4", "c4gqa"):
             try:
                 ow = WORKLOADS[other]
                 osets = make_inputs(torch, ow, 3, dev, copies=1)
                 osec = time_device(torch, fa, other, ow, osets, 5 if other == "c4" else 10, 3, 0, lambda: None)
                 of, ob = work_per_step(other, ow)
-                if other == "c4":
+                if other.startswith("c4"):
                     side[other] = {"workload": ow["desc"], "ms": osec * 1e3, "gbs": ob / osec / 1e9,
                                    "frac_of_hbm_peak": ob / osec / 1e9 / peaks["hbm"]}
                 else:
