@@ -177,6 +177,15 @@ bool tma_epilogue_enabled() {
     return on;
 }
 
+// Development switch: FA_B200_DECODE_SHORTQ=0 sends 2 <= seqlen_q <= 8 through the tiled kernel.
+bool decode_short_q_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("FA_B200_DECODE_SHORTQ");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 size_t partial_bytes(const fa_fwd_params* p, int splits, size_t* lse_off) {
     const size_t rows = static_cast<size_t>(p->batch) * p->heads * splits * p->seqlen_q;
     const size_t o_bytes = (rows * p->head_dim * sizeof(float) + 255) & ~static_cast<size_t>(255);
@@ -322,14 +331,14 @@ int fa_fwd(const fa_fwd_params* p) {
     CUtensorMap to = tq;
     a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32 && tma_epilogue_enabled()) ? 1 : 0;
     if (a.o_tma && (rc = make_tensor_map(&to, bf16, p->o, p->head_dim, p->seqlen_q, units, 32)) != FA_OK) return rc;
-    if (p->seqlen_q == 1 && decode_kernel_enabled()) {
-        // one query row per unit: the streaming kernel with keys on the tensor-memory lanes
+    if (decode_kernel_enabled() && (p->seqlen_q == 1 || (p->seqlen_q <= 8 && decode_short_q_enabled()))) {
+        // one to eight query rows per unit: the streaming kernel with keys on the tensor-memory lanes
         DecodeArgs d;
         std::memset(&d, 0, sizeof(d));
         d.q = p->q; d.o = p->o; d.lse = p->lse;
         d.o_partial = a.o_partial; d.lse_partial = a.lse_partial;
         d.alibi_slopes = p->alibi_slopes; d.status = p->status;
-        d.heads = p->heads; d.kv_group = a.kv_group; d.seqlen_k = p->seqlen_k; d.head_dim = p->head_dim; d.tc = a.tc;
+        d.heads = p->heads; d.kv_group = a.kv_group; d.seqlen_q = p->seqlen_q; d.seqlen_k = p->seqlen_k; d.head_dim = p->head_dim; d.tc = a.tc;
         d.num_splits = splits; d.tiles_per_split = a.tiles_per_split; d.scale_log2 = a.scale_log2;
         d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
         d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;

@@ -15,11 +15,12 @@
 // The MMAs are tiny (N = 16): the tensor pipe is a convenient dot-product engine that
 // reads K/V straight from the swizzled TMA tiles, and the kernel stays HBM-bound.
 //
-// Grouped-query attention (kH = 8): the query heads that share one K/V head ride in columns
-// 0..7 of the same MMAs (rows 0..7 of the Q and P operand tiles), so a CTA streams its K/V
-// split once for up to eight heads; every per-query quantity (max, sum, ALiBi slope, dropout
-// stream, LSE) becomes an array over the heads.  Groups larger than eight are cut into
-// sub-groups of eight heads, one CTA each.
+// Grouped-query attention and short query blocks (kH = 8): the query heads that share one K/V
+// head, and the seqlen_q <= 8 query rows of each, ride in columns 0..7 of the same MMAs (rows
+// 0..7 of the Q and P operand tiles; column = head * seqlen_q + row), so a CTA streams its K/V
+// split once for up to eight queries; every per-query quantity (position, masks, max, sum, ALiBi
+// slope, dropout stream, LSE) becomes an array over the columns.  Groups that need more than
+// eight columns are cut into sub-groups of whole heads, one CTA each.
 //
 // Stream order of the TMA ring: K(0), K(1), V(0), K(2), V(1), ... (chunks of four tiles), so
 // the scores of chunk c+1 are computed while the softmax of chunk c runs.
@@ -124,29 +125,32 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
     const int cta_unit = blockIdx.x / a.num_splits;
     const int split = blockIdx.x - cta_unit * a.num_splits;
     int unit, kv_unit, gh = 1;
+    const int sq = (kH == 1) ? 1 : a.seqlen_q;  // query rows per head (columns per head)
     if constexpr (kH == 1) {
         unit = cta_unit;
         kv_unit = a.kv_group > 1 ? unit / a.kv_group : unit;
     } else {
+        const int heads_per_cta = kH / sq;
         kv_unit = cta_unit / a.subgroups;
         const int sub = cta_unit - kv_unit * a.subgroups;
-        unit = kv_unit * a.kv_group + sub * kH;
-        gh = min(kH, a.kv_group - sub * kH);  // query heads of this CTA
+        unit = kv_unit * a.kv_group + sub * heads_per_cta;
+        gh = min(heads_per_cta, a.kv_group - sub * heads_per_cta);  // query heads of this CTA
     }
+    const int nc = gh * sq;  // columns in use: column n = head n / sq, query row n % sq
 
     // KV tiles of this split, clipped by the masks at tile granularity (as kv_tile_range
-    // of the tiled kernel, for the single query row at position q_pos0)
+    // of the tiled kernel, for the query rows at positions q_pos0 .. q_pos0 + sq - 1)
     int lo = a.tiles_per_split * split, hi = min(lo + a.tiles_per_split, a.tc);
     if (a.window_left >= 0) {
         const long long w = (a.q_pos0 - a.window_left - a.k_pos0) / kTile;
         lo = max(lo, static_cast<int>(max(0LL, min(w, static_cast<long long>(a.tc)))));
     }
     if (a.window_right >= 0) {
-        const long long last = a.q_pos0 + a.window_right - a.k_pos0;
+        const long long last = a.q_pos0 + (sq - 1) + a.window_right - a.k_pos0;
         hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
     }
     if (a.is_causal) {
-        const long long last = a.q_pos0 - a.k_pos0;
+        const long long last = a.q_pos0 + (sq - 1) - a.k_pos0;
         hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
     }
     const int n_tiles = hi > lo ? hi - lo : 0;
@@ -173,12 +177,13 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         tmem_relinquish();
     }
     if (threadIdx.x < 16 * kH && n_tiles > 0) {
-        // query head n goes to row n of the two Q atoms (16-byte unit u -> atom u/8, unit (u%8) ^ n:
-        // the 128-byte swizzle of row n)
+        // query n (head n / sq, row n % sq: consecutive rows of Q) goes to row n of the two Q atoms
+        // (16-byte unit u -> atom u/8, unit (u%8) ^ n: the 128-byte swizzle of row n)
         const int u = threadIdx.x & 15, n = threadIdx.x >> 4;
         uint4 val = make_uint4(0u, 0u, 0u, 0u);
-        if (n < gh && u * 8 < a.head_dim)
-            val = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.q) + static_cast<long long>(unit + n) * a.head_dim + u * 8);
+        if (n < nc && u * 8 < a.head_dim)
+            val = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(a.q) +
+                                                  (static_cast<long long>(unit) * sq + n) * a.head_dim + u * 8);
         *reinterpret_cast<uint4*>(smem_gen + kDSmemQ + (u >> 3) * 1024 + n * 128 + (((u & 7) ^ n) << 4)) = val;
         fence_proxy_async_smem();
     }
@@ -283,9 +288,12 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         const float scale2 = a.scale_log2;
         float slope2[kH];
+        int qrow[kH];  // each column's query row; its global position is q_pos0 + qrow
 #pragma unroll
-        for (int n = 0; n < kH; ++n)
-            slope2[n] = (a.alibi_slopes != nullptr && n < gh) ? a.alibi_slopes[(unit + n) % a.heads] * kDLog2e : 0.0f;
+        for (int n = 0; n < kH; ++n) {
+            slope2[n] = (a.alibi_slopes != nullptr && n < nc) ? a.alibi_slopes[(unit + n / sq) % a.heads] * kDLog2e : 0.0f;
+            qrow[n] = (kH == 1) ? 0 : n % sq;
+        }
         const bool dropout = a.drop.threshold != 0ull;
         float m_ref[kH];   // CTA-wide running max per head, log2 units
         float l_part[kH];  // this thread's share of each head's row sum
@@ -324,15 +332,19 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
                 const int tile = lo + c * kChunkTiles + t;
                 const long long key = static_cast<long long>(tile) * kTile + r;
                 const long long kpos = a.k_pos0 + key;
-                bool keep = t < nt && key < a.seqlen_k;
-                if (a.is_causal && kpos > a.q_pos0) keep = false;
-                if (a.window_left >= 0 && a.q_pos0 - kpos > a.window_left) keep = false;
-                if (a.window_right >= 0 && kpos - a.q_pos0 > a.window_right) keep = false;
-                const float dist = fabsf(static_cast<float>(a.q_pos0 - kpos));
+                const bool in_range = t < nt && key < a.seqlen_k;
+                // key position relative to query row 0, saturated far outside any window
+                const long long rel64 = kpos - a.q_pos0;
+                const int rel = static_cast<int>(max(-0x40000000LL, min(rel64, 0x40000000LL)));
 #pragma unroll
                 for (int n = 0; n < kH; ++n) {
+                    const int ahead = rel - qrow[n];  // > 0: the key lies after the query
+                    bool keep = in_range;
+                    if (a.is_causal && ahead > 0) keep = false;
+                    if (a.window_left >= 0 && -ahead > a.window_left) keep = false;
+                    if (a.window_right >= 0 && ahead > a.window_right) keep = false;
                     float sc = v[t][n] * scale2;
-                    if (slope2[n] != 0.0f) sc = fmaf(-slope2[n], dist, sc);
+                    if (slope2[n] != 0.0f) sc = fmaf(-slope2[n], fabsf(static_cast<float>(ahead)), sc);
                     v[t][n] = keep ? sc : -INFINITY;
                     m_thr[n] = fmaxf(m_thr[n], v[t][n]);
                 }
@@ -387,10 +399,11 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
                         const float p = ex2f(v[t][n] - m_use[n]);
                         l_part[n] += p;
                         bool kept = true;
-                        if (dropout && n < gh) {
-                            // reference draw order for query row 0: draw 64*tile_index + 8*(col/16) + 2*((col%16)/8) + col%2
+                        if (dropout && n < nc) {
+                            // reference draw order for query rows 0..7 (one 8-row group shares its draws):
+                            // draw 64*tile_index + 8*(col/16) + 2*((col%16)/8) + col%2
                             const unsigned long long subseq =
-                                (a.drop.unit0 + unit + n) * static_cast<unsigned long long>(a.num_splits) +
+                                (a.drop.unit0 + unit + n / sq) * static_cast<unsigned long long>(a.num_splits) +
                                 static_cast<unsigned long long>(split);
                             const unsigned long long first = 64ull * static_cast<unsigned long long>(c * kChunkTiles + t) +
                                                              8ull * (r >> 4);
@@ -436,12 +449,14 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
         }
 #pragma unroll
         for (int n = 0; n < kH; ++n) {
-            if (n >= gh) continue;
+            if (n >= nc) continue;
             const float l_sum = (red[64 + n] + red[64 + 8 + n]) + (red[64 + 16 + n] + red[64 + 24 + n]);
             const float inv = l_sum > 0.0f ? a.drop.inv_keep / l_sum : 0.0f;
             const float lse_val = l_sum > 0.0f ? m_ref[n] * kDLn2 + __logf(l_sum) : -INFINITY;
             const float o_val = __uint_as_float(o_raw[n]) * inv;
-            const long long out_row = (a.num_splits > 1) ? static_cast<long long>(unit + n) * a.num_splits + split : unit + n;
+            // non-split: row (unit + head, query row) of O; split: the same row of this split's partial
+            const long long head_n = unit + n / sq;
+            const long long out_row = (a.num_splits > 1) ? (head_n * a.num_splits + split) * sq + n % sq : head_n * sq + n % sq;
             if (r < a.head_dim) {
                 if (a.num_splits > 1) a.o_partial[out_row * a.head_dim + r] = o_val;
                 else if (a.o_is_fp32) static_cast<float*>(a.o)[out_row * a.head_dim + r] = o_val;
@@ -482,8 +497,10 @@ cudaError_t launch_decode(const DecodeArgs& a_in, const CUtensorMap& tk, const C
     // query heads that share a K/V head are packed into one CTA, eight at a time
     // (development switch: FA_B200_DECODE_PACK=0 keeps one CTA per query head)
     static const bool allow_pack = [] { const char* e = std::getenv("FA_B200_DECODE_PACK"); return !(e && e[0] == '0'); }();
-    const bool packed = a.kv_group > 1 && allow_pack;
-    a.subgroups = packed ? (a.kv_group + 7) / 8 : 1;
+    if (a.seqlen_q < 1 || a.seqlen_q > 8) return cudaErrorInvalidValue;
+    const bool packed = (a.kv_group > 1 && allow_pack) || a.seqlen_q > 1;
+    const int heads_per_cta = 8 / a.seqlen_q;  // whole heads whose query rows fit the eight columns
+    a.subgroups = packed ? (a.kv_group + heads_per_cta - 1) / heads_per_cta : 1;
     const long long cta_units = packed ? static_cast<long long>(units / a.kv_group) * a.subgroups : units;
     const long long ctas = cta_units * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;

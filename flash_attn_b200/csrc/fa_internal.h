@@ -49,7 +49,8 @@ struct DecodeArgs {
     int* status;
     int heads;
     int kv_group;           // query units per K/V unit; K/V unit = unit / kv_group
-    int subgroups;          // CTAs (of up to eight query heads) per K/V unit when kv_group > 1; set by launch_decode
+    int subgroups;          // CTAs (of up to eight query columns) per K/V unit on the packed path; set by launch_decode
+    int seqlen_q;           // query rows per unit, 1..8
     int seqlen_k, head_dim;
     int tc;
     int num_splits, tiles_per_split;

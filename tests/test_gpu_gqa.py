@@ -46,6 +46,23 @@ def test_gqa_decode_dropout_alibi_window_fp16():
     gpu_util.assert_close(res, "gqa decode dropout alibi window")
 
 
+@pytest.mark.parametrize("H,Hk,Nq,splits", [(4, 4, 4, 3), (8, 2, 2, 2), (4, 2, 3, 1), (8, 1, 8, 4), (2, 2, 8, 1), (6, 3, 5, 2)])
+def test_short_query_blocks_on_the_decode_kernel(H, Hk, Nq, splits):
+    # 2..8 query rows per head (bottom-right causal: the last rows of the sequence), packed with the
+    # heads of a K/V group into the eight columns of the decode kernel
+    Nk = 1300
+    res = gpu_util.run_case(2, H, Nq, Nk, 128, heads_k=Hk, num_splits=splits, q_pos0=Nk - Nq, causal=True, seed=19)
+    gpu_util.assert_close(res, f"short q H={H} Hk={Hk} Nq={Nq} splits={splits}")
+
+
+def test_short_query_dropout_alibi_window_fp16():
+    res = gpu_util.run_case(1, 4, 5, 900, 64, dtype="float16", heads_k=2, num_splits=2, q_pos0=895, causal=True,
+                            window=(500, 0), alibi=True, p_dropout=0.2, seed=20)
+    gpu_util.assert_close(res, "short q dropout alibi window")
+    res = gpu_util.run_case(1, 2, 7, 640, 128, q_pos0=100, causal=True, p_dropout=0.1, seed=21)  # rows that see few keys
+    gpu_util.assert_close(res, "short q early rows")
+
+
 def test_gqa_host_buffers():
     res = gpu_util.run_case(3, 6, 256, 256, 128, causal=True, heads_k=2, host=True, seed=16)
     gpu_util.assert_close(res, "gqa host path")
