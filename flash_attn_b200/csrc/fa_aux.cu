@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include "../../include/fa_b200.h"
 #include "fa_internal.h"
+#include "sm100_ptx.cuh"
 
 namespace fa {
 
@@ -23,6 +24,9 @@ __device__ __forceinline__ void store_out(void* o, int o_dtype, long long idx, f
 // O = sum_j exp(lse_j - lse) O_j, the reference's (M, L) algebra with
 // lse_j = M_j + log L_j folded into one number per split.
 __global__ void combine_kernel(const CombineArgs a, long long total_rows) {
+    // launched with programmatic stream serialization behind the kernel that writes the partials:
+    // the CTAs are resident and waiting when that kernel ends
+    grid_dep_wait();
     const long long row = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (row >= total_rows) return;
@@ -138,8 +142,16 @@ cudaError_t launch_combine(const CombineArgs& a, long long units, cudaStream_t s
     if (rows <= 0) return cudaSuccess;
     const int threads = 256;
     const long long blocks = (rows * 32 + threads - 1) / threads;
-    combine_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(a, rows);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, combine_kernel, a, rows);
 }
 
 cudaError_t launch_merge(float* o_acc, float* lse_acc, const void* o_part, const float* lse_part, int part_dtype,

@@ -120,6 +120,9 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // the combine kernel behind a split launch may take its place on the SMs as they free up
+    // (it waits for this grid's completion before reading the partials)
+    grid_dep_launch_dependents();
     // kH = 1: one CTA per (query unit, split).  kH = 8: one CTA per (K/V unit, sub-group of up to
     // eight of its query heads, split); `unit` is then the first query unit of the sub-group.
     const int cta_unit = blockIdx.x / a.num_splits;

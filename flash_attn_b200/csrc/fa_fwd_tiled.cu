@@ -284,6 +284,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     FA_TR(90);
 #endif
 
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up as
+    // soon as SMs free up, and do this kernel's set-up (index arithmetic, barriers, TMEM) before
+    // waiting for the kernel in front of it; no global memory is touched before grid_dep_wait().
+    grid_dep_launch_dependents();
+
     // ---- which query tiles does this CTA own ------------------------------------
     const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
     const int per_unit = trq * a.num_splits;
@@ -333,6 +338,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(bar_v_empty + 8 * s, 1);
         }
         mbar_fence_init();
+        grid_dep_wait();
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
@@ -369,6 +375,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
         tmem_relinquish();
     }
+    grid_dep_wait();  // every thread, before its first global access (the producer lane has passed it already)
     FA_TR(92);
     tc_fence_before_sync();
     __syncthreads();
@@ -823,8 +830,20 @@ cudaError_t launch_one(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMa
     const int trq = (a.tr + NQ - 1) / NQ;
     const long long ctas = static_cast<long long>(units) * trq * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    kern<<<static_cast<unsigned>(ctas), Cfg<D, NQ>::kThreads, smem, stream>>>(tq, tk, tv, to, a);
-    return cudaGetLastError();
+    // launched with programmatic stream serialization: the kernel may begin its set-up while the
+    // kernel before it in the stream drains (development switch FA_B200_PDL=0 launches plainly)
+    static const bool pdl = [] { const char* e = std::getenv("FA_B200_PDL"); return !(e && e[0] == '0'); }();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
+    cfg.blockDim = dim3(Cfg<D, NQ>::kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, to, a);
 }
 
 template <int D, int NQ, bool kBf16>
