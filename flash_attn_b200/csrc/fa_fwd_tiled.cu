@@ -589,9 +589,23 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if constexpr (kAlibi) {
                 const float dist0 = static_cast<float>(qpos - kbase);
                 if (keys_not_after) {
+                    // bias of column c = slope*(c - dist0), built up pair by pair (one packed add and
+                    // one packed FMA per two columns); the running sum is re-based every 16 columns
                     const float base = -slope2 * dist0;
+                    const float2 step2 = make_float2(2.0f * slope2, 2.0f * slope2);
+                    const float2 sc2 = make_float2(scale2, scale2);
 #pragma unroll
-                    for (int c = 0; c < 128; ++c) s[c] = fmaf(s[c], scale2, fmaf(slope2, static_cast<float>(c), base));
+                    for (int c0 = 0; c0 < 128; c0 += 16) {
+                        float2 bias2 = make_float2(fmaf(slope2, static_cast<float>(c0), base),
+                                                   fmaf(slope2, static_cast<float>(c0 + 1), base));
+#pragma unroll
+                        for (int c = c0; c < c0 + 16; c += 2) {
+                            const float2 v2 = __ffma2_rn(make_float2(s[c], s[c + 1]), sc2, bias2);
+                            s[c] = v2.x;
+                            s[c + 1] = v2.y;
+                            bias2 = __fadd2_rn(bias2, step2);
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < 128; ++c) s[c] = fmaf(-slope2, fabsf(dist0 - static_cast<float>(c)), s[c] * scale2);
