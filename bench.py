@@ -66,7 +66,8 @@ def attended_pairs(w):
 
 
 def work_per_step(name, w):
-    """(flops, bytes) of one step on one GPU, by the conventions stated in DESIGN.md."""
+    """(flops, bytes) of one step on one GPU: 4*d FLOP per attended (query, key) pair (causal configs by the
+    4*B*H*N^2*d/2 convention), bytes = K + V + Q + O in 16-bit."""
     units = w["B"] * w["H"]
     if name in ("c2", "c5"):
         flops = 4.0 * units * w["Nq"] * w["Nk"] * w["d"] / 2  # causal convention 4*B*H*N^2*d/2
