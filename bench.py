@@ -369,7 +369,8 @@ def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, 
         "clocks": clocks,
         "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                 "note": "the ring works on device-resident shards; the host-buffer path is measured on config 2"},
-        "gpu_launches": (1 if use_a2a else 2 * pairs + 2) * args.steps * world,
+        # all-to-all: one forward launch per head group; ring: forward + merge per visited pair, two casts
+        "gpu_launches": (ulysses._head_groups(w["H"], w["H"], world, 4) if use_a2a else 2 * pairs + 2) * args.steps * world,
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tensor_sustained"] or peaks["tensor"],
                      "unit": "TFLOP/s", "frac": value / world / (peaks["tensor_sustained"] or peaks["tensor"]),
                      "peak_source": peaks["source"] + " sustained (seconds-long step)", "traffic": None,
