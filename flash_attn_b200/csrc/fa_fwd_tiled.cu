@@ -887,7 +887,9 @@ cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUte
     // shapes) keeps two independent CTAs per SM instead
     // (development switch: FA_B200_PAIR=0 runs one query tile per CTA, two CTAs per SM, throughout)
     static const bool allow_pair = [] { const char* e = std::getenv("FA_B200_PAIR"); return !(e && e[0] == '0'); }();
-    const bool pair = a.tr >= 2 && allow_pair;
+    // (with two query tiles and a causal mask the pair would spend half its time on the diagonal tile that
+    // only one of them can use: 277 against 308 TFLOP/s at [128,16,256,128])
+    const bool pair = (a.tr > 2 || (a.tr == 2 && !a.is_causal)) && allow_pair;
     if (a.head_dim <= 64) {
         return pair ? launch_dtype<64, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream)
                     : launch_dtype<64, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream);
