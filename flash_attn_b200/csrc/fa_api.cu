@@ -2,8 +2,8 @@
 // tensor maps and kernel dispatch.  This is the successor of the launcher block
 // of the reference's main() (src/main.cu:109-205) with every compile-time switch
 // (src/main.cu:39-49) turned into a run-time parameter.
+#include <atomic>
 #include <cmath>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -98,16 +98,19 @@ unsigned long long keep_threshold(float p) {
 int sm_count_of_current_device(int* sms, int* major) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return FA_ERR_CUDA;
-    static int cached_sms[64] = {};
-    static int cached_major[64] = {};
-    if (dev >= 0 && dev < 64 && cached_sms[dev] > 0) {
-        *sms = cached_sms[dev];
-        *major = cached_major[dev];
-        return FA_OK;
+    // (SM count << 8 | major) per device ordinal, 0 = not asked yet; concurrent first calls store the same value
+    static std::atomic<int> cached[64];
+    if (dev >= 0 && dev < 64) {
+        const int c = cached[dev].load(std::memory_order_relaxed);
+        if (c > 0) {
+            *sms = c >> 8;
+            *major = c & 0xff;
+            return FA_OK;
+        }
     }
     if (cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return FA_ERR_CUDA;
     if (cudaDeviceGetAttribute(major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return FA_ERR_CUDA;
-    if (dev >= 0 && dev < 64) { cached_sms[dev] = *sms; cached_major[dev] = *major; }
+    if (dev >= 0 && dev < 64) cached[dev].store((*sms << 8) | (*major & 0xff), std::memory_order_relaxed);
     return FA_OK;
 }
 
@@ -180,33 +183,6 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->drop.unit0 = p->unit0;
     a->drop.threshold = p->p_dropout > 0.0f ? keep_threshold(p->p_dropout) : 0ull;
     a->drop.inv_keep = p->p_dropout > 0.0f ? 1.0f / (1.0f - p->p_dropout) : 1.0f;
-}
-
-// Development switch: FA_B200_DECODE=0 sends seqlen_q = 1 launches through the tiled kernel.
-bool decode_kernel_enabled() {
-    static const bool on = [] {
-        const char* e = std::getenv("FA_B200_DECODE");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
-
-// Development switch: FA_B200_TMA_STORE=0 writes O with per-thread global stores throughout.
-bool tma_epilogue_enabled() {
-    static const bool on = [] {
-        const char* e = std::getenv("FA_B200_TMA_STORE");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
-
-// Development switch: FA_B200_DECODE_SHORTQ=0 sends 2 <= seqlen_q <= 8 through the tiled kernel.
-bool decode_short_q_enabled() {
-    static const bool on = [] {
-        const char* e = std::getenv("FA_B200_DECODE_SHORTQ");
-        return !(e && e[0] == '0');
-    }();
-    return on;
 }
 
 size_t partial_bytes(const fa_fwd_params* p, int splits, size_t* lse_off) {
@@ -352,9 +328,9 @@ int fa_fwd(const fa_fwd_params* p) {
     if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units_k)) != FA_OK) return rc;
     // 16-bit output of an unsplit launch is written by TMA stores, one 32-row box per warp
     CUtensorMap to = tq;
-    a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32 && tma_epilogue_enabled()) ? 1 : 0;
+    a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32) ? 1 : 0;
     if (a.o_tma && (rc = make_tensor_map(&to, bf16, p->o, p->head_dim, p->seqlen_q, units, 32)) != FA_OK) return rc;
-    if (decode_kernel_enabled() && (p->seqlen_q == 1 || (p->seqlen_q <= 8 && decode_short_q_enabled()))) {
+    if (p->seqlen_q <= 8) {
         // one to eight query rows per unit: the streaming kernel with keys on the tensor-memory lanes
         DecodeArgs d;
         std::memset(&d, 0, sizeof(d));
@@ -366,7 +342,7 @@ int fa_fwd(const fa_fwd_params* p) {
         d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
         d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;
         if (launch_decode(d, tk, tv, units, bf16, stream) != cudaSuccess) return FA_ERR_CUDA;
-    } else if (launch_fwd_tiled(a, tq, tk, tv, to, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) {
+    } else if (launch_fwd_tiled(a, tq, tk, tv, to, units, bf16, p->p_dropout > 0.0f, sms, stream) != cudaSuccess) {
         return FA_ERR_CUDA;
     }
     if (splits > 1) {

@@ -24,7 +24,7 @@
 //
 // Stream order of the TMA ring: K(0), K(1), V(0), K(2), V(1), ... (chunks of four tiles), so
 // the scores of chunk c+1 are computed while the softmax of chunk c runs.
-#include <cstdlib>
+#include <atomic>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "fa_internal.h"
@@ -492,26 +492,24 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
 
 cudaError_t launch_decode(const DecodeArgs& a_in, const CUtensorMap& tk, const CUtensorMap& tv, int units, bool bf16,
                           cudaStream_t stream) {
-    static bool configured[4][64] = {};
+    static std::atomic<bool> configured[4][64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     DecodeArgs a = a_in;
     // query heads that share a K/V head are packed into one CTA, eight at a time
-    // (development switch: FA_B200_DECODE_PACK=0 keeps one CTA per query head)
-    static const bool allow_pack = [] { const char* e = std::getenv("FA_B200_DECODE_PACK"); return !(e && e[0] == '0'); }();
     if (a.seqlen_q < 1 || a.seqlen_q > 8) return cudaErrorInvalidValue;
-    const bool packed = (a.kv_group > 1 && allow_pack) || a.seqlen_q > 1;
+    const bool packed = a.kv_group > 1 || a.seqlen_q > 1;
     const int heads_per_cta = 8 / a.seqlen_q;  // whole heads whose query rows fit the eight columns
     a.subgroups = packed ? (a.kv_group + heads_per_cta - 1) / heads_per_cta : 1;
     const long long cta_units = packed ? static_cast<long long>(units / a.kv_group) * a.subgroups : units;
     const long long ctas = cta_units * a.num_splits;
     if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     auto run = [&](auto kern, int which) -> cudaError_t {
-        if (dev < 0 || dev >= 64 || !configured[which][dev]) {
+        if (dev < 0 || dev >= 64 || !configured[which][dev].load(std::memory_order_acquire)) {
             cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kDSmemBytes);
             if (err != cudaSuccess) return err;
-            if (dev >= 0 && dev < 64) configured[which][dev] = true;
+            if (dev >= 0 && dev < 64) configured[which][dev].store(true, std::memory_order_release);
         }
         kern<<<static_cast<unsigned>(ctas), kDThreads, kDSmemBytes, stream>>>(tk, tv, a);
         return cudaGetLastError();

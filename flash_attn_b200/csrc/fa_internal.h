@@ -9,6 +9,18 @@ namespace fa {
 
 constexpr int kTile = 128;  // Br = Bc = 128, as the reference fixes them (src/main.cu:116-117)
 
+// Division by a launch-constant divisor without the hardware's slow integer divide: the
+// quotient is mulhi(x, m) with m = floor(2^32 / d) + 1, which is floor(x / d) or one more.
+struct FastDiv {
+    uint32_t d, m;
+};
+inline FastDiv make_fastdiv(uint32_t d) {
+    FastDiv f;
+    f.d = d < 1 ? 1 : d;
+    f.m = f.d == 1 ? 0u : static_cast<uint32_t>((1ull << 32) / f.d) + 1u;
+    return f;
+}
+
 // Device-side argument block of the tiled forward kernel (the successor of
 // mykernelParamType, include/utils.h:21-44).  Q/K/V travel as TMA tensor maps.
 struct FwdArgs {
@@ -30,13 +42,18 @@ struct FwdArgs {
     long long q_pos0, k_pos0;
     int o_is_fp32;
     int o_tma;              // O leaves through the TMA store map (16-bit output, unsplit launch)
+    // launch order of the work items (filled by launch_fwd_tiled)
+    int n_items;            // units * query blocks * splits
+    int sched_slot;         // persistent kernel: which claim counter this launch uses, and
+    uint32_t sched_tag;     // the tag that marks the counter as this launch's
+    FastDiv div_group_items, div_gsize, div_last_gsize, div_splits;
     DropoutParams drop;
 };
 
 // Launchers implemented in the .cu files; all return a cudaError_t.  `to` is the store map of O
 // (32-row boxes); it is read only when a.o_tma is set.
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                             const CUtensorMap& to, int units, bool bf16, bool dropout, cudaStream_t stream);
+                             const CUtensorMap& to, int units, bool bf16, bool dropout, int sms, cudaStream_t stream);
 
 // Device-side argument block of the decode kernel (seqlen_q = 1).
 struct DecodeArgs {
