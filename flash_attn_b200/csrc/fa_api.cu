@@ -342,7 +342,7 @@ int fa_fwd(const fa_fwd_params* p) {
         d.is_causal = a.is_causal; d.window_left = a.window_left; d.window_right = a.window_right;
         d.q_pos0 = a.q_pos0; d.k_pos0 = a.k_pos0; d.o_is_fp32 = a.o_is_fp32; d.drop = a.drop;
         if (launch_decode(d, tk, tv, units, bf16, stream) != cudaSuccess) return FA_ERR_CUDA;
-    } else if (launch_fwd_tiled(a, tq, tk, tv, to, units, bf16, p->p_dropout > 0.0f, sms, stream) != cudaSuccess) {
+    } else if (launch_fwd_tiled(a, tq, tk, tv, to, units, bf16, p->p_dropout > 0.0f, stream) != cudaSuccess) {
         return FA_ERR_CUDA;
     }
     if (splits > 1) {

@@ -2,7 +2,7 @@
 // forward_kernel (src/flash_forward.h:13-306) and forward_kernel_splitkv
 // (src/flash_forward_splitkv.h:14-344).
 //
-// A work item is NQ (1 or 2) consecutive 128-row query tiles of one (batch, head)
+// A CTA owns NQ (1 or 2) consecutive 128-row query tiles of one (batch, head)
 // unit, optionally one KV split of them; each query tile is exactly one CTA of
 // the reference's decomposition (grid (Tr*splits, H, B), src/main.cu:142-158),
 // which is what the dropout streams are keyed on.  Roles by warp:
@@ -10,27 +10,18 @@
 //       from tensor memory (tcgen05.ld), masked / biased / exponentiated in
 //       registers, the 16-bit P is written back to tensor memory over S
 //       (tcgen05.st); the running (max, sum) and the lazy rescale of O live here.
-//   TMA producer warp: streams the Q tiles and the K/V tiles through mbarrier
-//       rings (cp.async.bulk.tensor, 128-byte swizzle).
+//   TMA producer warp: streams the Q tiles once and K/V tiles through an mbarrier
+//       ring (cp.async.bulk.tensor, 128-byte swizzle).
 //   MMA issuer warp: one thread issues tcgen05.mma for S_i = Q_i K^T (operands in
 //       shared memory) and O_i += P_i V (P in tensor memory, V in shared memory,
 //       MN-major), accumulators in tensor memory.  With NQ = 2 the two query tiles
 //       alternate on the tensor pipe, so the softmax of one overlaps the MMAs of
 //       the other while both share every K/V tile brought in by TMA.
-// NQ = 1 (units of one or two query tiles): one CTA per item, two CTAs per SM.
-// NQ = 2: a persistent kernel, one CTA per SM, which walks a list of items that the
-// host scheduled for it (FwdSched).  TMEM, the barriers and the K/V ring live across
-// items: the K/V tiles of consecutive items form one stream, the Q tiles of the next
-// item are fetched as soon as the last Q K^T of the current one has been issued, the
-// first Q K^T of the next item is issued behind the last P V of the current one, and O
-// leaves through a small staging buffer per warp, so that a query tile's epilogue
-// overlaps the other tile's tensor work instead of an empty SM.
 // KV tiles are visited from the last to the first (the softmax is order-independent and the
-// dropout draw of an element is a function of its position): with a causal mask the odd
-// query tile of an item owns one KV tile more than the even one, the diagonal one, and
-// walking backwards puts that solo tile at the start of the item.  The odd tile belongs to
-// the softmax group that the MMA warp serves first, which is the group that finishes an
-// item first: it runs the next item's solo tile while the other group is still finishing.
+// dropout draw of an element is a function of its position): with a causal mask the second
+// query tile of a CTA owns one KV tile more than the first, the diagonal one, and walking
+// backwards puts that solo tile at the start, where it overlaps the first tile of the other
+// query tile, instead of at the end, where the other warpgroup would idle.
 // The reference keeps O in shared memory and renormalises it every tile
 // (src/flash_forward.h:248-290); here O stays un-normalised in tensor memory and
 // is divided by the row sum once, in the epilogue.
@@ -49,43 +40,20 @@
 #ifndef FA_TRACE_CTA
 #define FA_TRACE_CTA 0
 #endif
-__device__ long long fa_trace_buf[16 * 4096];
-__device__ unsigned int fa_claims[256 * 64];  // per CTA: the positions it claimed, in order
-extern "C" int fa_claims_read(unsigned int* host_out) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_claims, sizeof(fa_claims)));
-}
-__device__ unsigned long long fa_cta_times[4 * 1024];  // per CTA: start, past the grid dependency wait, roles done, end (ns)
-extern "C" int fa_cta_times_read(unsigned long long* host_out) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_cta_times, sizeof(fa_cta_times)));
-}
-__device__ __forceinline__ unsigned long long fa_globaltimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define FA_CTA_TIME(k)                                                                          \
-    do {                                                                                       \
-        if (threadIdx.x == 0 && blockIdx.x < 1024) fa_cta_times[4 * blockIdx.x + (k)] = fa_globaltimer(); \
-    } while (0)
-extern "C" int fa_trace_reset() {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, fa_trace_buf) != cudaSuccess) return -1;
-    return static_cast<int>(cudaMemset(p, 0, sizeof(long long) * 16 * 4096));
-}
+__device__ long long fa_trace_buf[16 * 512];
 extern "C" int fa_trace_read(long long* host_out) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_trace_buf, sizeof(long long) * 16 * 4096));
+    return static_cast<int>(cudaMemcpyFromSymbol(host_out, fa_trace_buf, sizeof(long long) * 16 * 512));
 }
 #define FA_TR(ev)                                                                              \
     do {                                                                                       \
-        if (blockIdx.x == FA_TRACE_CTA && (threadIdx.x & 31) == 0 && tr_n < 2047) {                        \
-            fa_trace_buf[(threadIdx.x >> 5) * 4096 + 2 * tr_n] = (ev);                          \
-            fa_trace_buf[(threadIdx.x >> 5) * 4096 + 2 * tr_n + 1] = clock64();                 \
+        if (blockIdx.x == FA_TRACE_CTA && (threadIdx.x & 31) == 0 && tr_n < 255) {                        \
+            fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n] = (ev);                          \
+            fa_trace_buf[(threadIdx.x >> 5) * 512 + 2 * tr_n + 1] = clock64();                 \
             ++tr_n;                                                                            \
         }                                                                                      \
     } while (0)
 #else
 #define FA_TR(ev) do { } while (0)
-#define FA_CTA_TIME(k) do { } while (0)
 #endif
 
 namespace fa {
@@ -99,7 +67,6 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 template <int D, int NQ>
 struct Cfg {
-    static constexpr bool kPersist = NQ == 2;  // two query tiles per item: persistent kernel, one CTA per SM
     // The helper warps (producer, MMA issuer) are rounded up to a full warpgroup so that registers
     // can be moved from it to the softmax warpgroups (setmaxnreg works on whole warpgroups).
     static constexpr int kThreads = NQ == 2 ? 384 : 256;
@@ -108,7 +75,7 @@ struct Cfg {
     // forever, hence the static_assert.
     // ptxas allots 168 registers per thread under __launch_bounds__(384, 1) and 128 under (256, 2)
     static constexpr int kRegsLaunch = NQ == 2 ? 168 : 128;
-    static constexpr int kRegsHelper = NQ == 2 ? 56 : 48;     // producer / MMA warpgroup after the hand-over
+    static constexpr int kRegsHelper = NQ == 2 ? 48 : 40;     // producer / MMA warpgroup after the hand-over
     static constexpr int kRegsSoftmax = NQ == 2 ? 224 : 208;  // softmax warpgroups after the hand-over
     static_assert(NQ * 128 * kRegsSoftmax + 128 * kRegsHelper <= kThreads * kRegsLaunch,
                   "register hand-over exceeds the CTA's allocation");
@@ -123,50 +90,14 @@ struct Cfg {
     static constexpr int kSmemQ = 0;
     static constexpr int kSmemK = NQ * kTileBytes;
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
-    // persistent kernel: every softmax warp stages its 32 output rows, one 64-column box at a
-    // time, in 4 KB of its own, so that the Q buffers are free for the next item's loads
-    static constexpr int kSmemStage = kSmemV + kStages * kTileBytes;
-    static constexpr int kStageBytes = kPersist ? NQ * 4 * 4096 : 0;
-    static constexpr int kSmemBar = kSmemStage + kStageBytes;
-    // persistent kernel: claimed items travel from the producer to the other roles through a ring
-    static constexpr int kItemSlots = 4;
-    static constexpr int kItemReaders = 1 + 4 * NQ;  // MMA warp + softmax warps
-    static constexpr int kNumBars = 4 * NQ + 4 * kStages + (kPersist ? 2 * kItemSlots : 0);
-    static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 4 * kItemSlots + 1024;  // + alignment slack
-    static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
+    static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
+    static constexpr int kNumBars = 1 + 2 * NQ + 4 * kStages;
+    static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
 };
 
 struct TileRange {
     int lo, hi;  // KV tiles [lo, hi)
 };
-
-__host__ __device__ __forceinline__ TileRange kv_tile_range(const FwdArgs& a, int rb, int split) {
-    if (rb >= a.tr) return {0, 0};
-    const long long q0 = a.q_pos0 + static_cast<long long>(rb) * kTile;
-    const long long tc = a.tc;
-    long long lo = 0, hi = tc;
-    if (a.num_splits > 1) {  // src/flash_forward_splitkv.h:40-43
-        lo = static_cast<long long>(a.tiles_per_split) * split;
-        hi = lo + a.tiles_per_split < tc ? lo + a.tiles_per_split : tc;
-    }
-    if (a.window_left >= 0) {  // src/flash_forward.h:39
-        long long w = (q0 - a.window_left - a.k_pos0) / kTile;  // truncating, like the reference
-        w = w < 0 ? 0 : (w > tc ? tc : w);
-        lo = lo > w ? lo : w;
-    }
-    if (a.window_right >= 0) {  // src/flash_forward.h:42-44
-        const long long last = q0 + kTile - 1 + a.window_right - a.k_pos0;
-        const long long h = last < 0 ? 0 : (last / kTile + 1 < tc ? last / kTile + 1 : tc);
-        hi = hi < h ? hi : h;
-    }
-    if (a.is_causal) {  // src/flash_forward.h:46-48
-        const long long last = q0 + kTile - 1 - a.k_pos0;
-        const long long h = last < 0 ? 0 : (last / kTile + 1 < tc ? last / kTile + 1 : tc);
-        hi = hi < h ? hi : h;
-    }
-    if (hi < lo) hi = lo;
-    return {static_cast<int>(lo), static_cast<int>(hi)};
-}
 
 __device__ __forceinline__ uint32_t fast_div(const FastDiv& f, uint32_t x) {
     if (f.d == 1) return x;
@@ -175,119 +106,28 @@ __device__ __forceinline__ uint32_t fast_div(const FastDiv& f, uint32_t x) {
     return q;
 }
 
-// Launch order of the items: groups of unit_group units; inside a group all units' first query
-// block, then all second ones, ...  With a causal mask the blocks are visited heaviest first, so
-// the launch is close to a longest-job-first schedule while the K/V working set of the items in
-// flight (one group) stays far below the L2 size.
-struct ItemPos {
-    int unit, kv_unit, qb, split;
-};
-template <int NQ>
-__host__ __device__ __forceinline__ ItemPos item_position(const FwdArgs& a, uint32_t p) {
-    const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
-#ifdef __CUDA_ARCH__
-    const uint32_t g = fast_div(a.div_group_items, p);
-#else
-    const uint32_t g = p / a.div_group_items.d;
-#endif
-    const int unit0 = static_cast<int>(g) * a.unit_group;
-    const uint32_t rem = p - g * a.div_group_items.d;
-    const bool full = unit0 + a.unit_group <= a.units;
-#ifdef __CUDA_ARCH__
-    const uint32_t bx = fast_div(full ? a.div_gsize : a.div_last_gsize, rem);
-#else
-    const uint32_t bx = rem / (full ? a.div_gsize.d : a.div_last_gsize.d);
-#endif
-    ItemPos it;
-    it.unit = unit0 + static_cast<int>(rem - bx * (full ? a.div_gsize.d : a.div_last_gsize.d));
-    it.kv_unit = a.kv_group > 1 ? it.unit / a.kv_group : it.unit;  // grouped-query attention: K/V head of this unit
-    uint32_t qb = bx;
-    it.split = 0;
-    if (a.num_splits > 1) {
-#ifdef __CUDA_ARCH__
-        qb = fast_div(a.div_splits, bx);
-#else
-        qb = bx / a.div_splits.d;
-#endif
-        it.split = static_cast<int>(bx - qb * a.div_splits.d);
+__device__ __forceinline__ TileRange kv_tile_range(const FwdArgs& a, int rb, int split) {
+    if (rb >= a.tr) return {0, 0};
+    const long long q0 = a.q_pos0 + static_cast<long long>(rb) * kTile;
+    int lo = 0, hi = a.tc;
+    if (a.num_splits > 1) {  // src/flash_forward_splitkv.h:40-43
+        lo = a.tiles_per_split * split;
+        hi = min(lo + a.tiles_per_split, a.tc);
     }
-    it.qb = a.is_causal ? trq - 1 - static_cast<int>(qb) : static_cast<int>(qb);  // heaviest query blocks first
-    return it;
-}
-
-// Query tile of softmax group i inside query block qb: the groups take the tiles in descending
-// order, so that group 0, which the MMA warp serves first, owns the tile with the diagonal.
-template <int NQ>
-__host__ __device__ __forceinline__ int tile_of_group(int qb, int i) {
-    return qb * NQ + (NQ - 1 - i);
-}
-
-template <int NQ>
-struct Item {
-    ItemPos pos;
-    TileRange r[NQ];  // KV tiles of each softmax group's query tile
-    int lo, hi;       // KV tiles streamed for the item: [lo, hi), empty when hi <= lo
-};
-template <int NQ>
-__host__ __device__ __forceinline__ Item<NQ> make_item(const FwdArgs& a, uint32_t p) {
-    Item<NQ> it;
-    it.pos = item_position<NQ>(a, p);
-    it.lo = 0x7fffffff;
-    it.hi = 0;
-#pragma unroll
-    for (int i = 0; i < NQ; ++i) {
-        it.r[i] = kv_tile_range(a, tile_of_group<NQ>(it.pos.qb, i), it.pos.split);
-        if (it.r[i].hi > it.r[i].lo) {
-            it.lo = it.r[i].lo < it.lo ? it.r[i].lo : it.lo;
-            it.hi = it.r[i].hi > it.hi ? it.r[i].hi : it.hi;
-        }
+    if (a.window_left >= 0) {  // src/flash_forward.h:39
+        const long long w = (q0 - a.window_left - a.k_pos0) / kTile;  // truncating, like the reference
+        lo = max(lo, static_cast<int>(max(0LL, min(w, static_cast<long long>(a.tc)))));
     }
-    if (it.hi <= it.lo) it.lo = it.hi = 0;
-    return it;
-}
-
-// Work distribution of the persistent kernel (NQ = 2).  The items of a launch form one list in
-// launch order; the CTAs claim them one at a time from a counter in global memory, so that an SM
-// that runs faster (the SMs of a B200 differ by several percent on this kernel, and a static
-// split of the list left the slowest 15 % behind the mean) simply takes more of them.
-//   The counter is one of kSchedSlots 64-bit words that belong to the library image; a launch is
-// given the next slot in turn and a tag that is unique in the process.  High word = tag of the
-// launch that owns the word, low word = claims made so far.  A claim adds one and finds either
-// its own tag in what the word held, or anything else (and then restarts the word at its own
-// tag): a word left behind by a launch that never finished therefore heals itself.  Every CTA makes exactly one claim
-// beyond the end of the list; the CTA whose claim is the last one of the launch zeroes the
-// word (tag 0 is never issued), which is what makes a captured launch replayable with the
-// tag it was captured with.  Two launches that share a slot must not overlap on the device:
-// with kSchedSlots in rotation that takes kSchedSlots launches in flight at once.
-constexpr int kSchedSlots = 256;
-__device__ unsigned long long g_sched_counter[kSchedSlots];
-constexpr uint32_t kNoItem = 0xffffffffu;
-
-__device__ __forceinline__ uint32_t claim_item(const FwdArgs& a) {
-    unsigned long long* ctr = &g_sched_counter[a.sched_slot];
-    const unsigned long long mine = static_cast<unsigned long long>(a.sched_tag) << 32;
-    // One atomic add per claim (a compare-and-swap loop on the one word serialises the CTAs: with
-    // 148 of them claiming at once only one attempt per round trip succeeds).
-    unsigned long long old = atomicAdd(ctr, 1ull);
-    if ((old >> 32) != a.sched_tag) {
-        // The word is not this launch's yet (the add above only disturbed a count nobody needs):
-        // install the tag, taking item 0, unless another CTA does so first.
-        for (int tries = 0;; ++tries) {
-            const unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(ctr);
-            if ((cur >> 32) == a.sched_tag) {
-                old = atomicAdd(ctr, 1ull);
-                break;
-            }
-            if (atomicCAS(ctr, cur, mine + 1) == cur) {
-                old = mine;
-                break;
-            }
-            if (tries > (1 << 16)) return kNoItem;  // (never seen: every failed attempt means another CTA's succeeded)
-        }
+    if (a.window_right >= 0) {  // src/flash_forward.h:42-44
+        const long long last = q0 + kTile - 1 + a.window_right - a.k_pos0;
+        hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
     }
-    const uint32_t n = static_cast<uint32_t>(old);
-    if (n + 1 == static_cast<uint32_t>(a.n_items) + gridDim.x) atomicExch(ctr, 0ull);  // the launch's last claim
-    return n < static_cast<uint32_t>(a.n_items) ? n : kNoItem;
+    if (a.is_causal) {  // src/flash_forward.h:46-48
+        const long long last = q0 + kTile - 1 - a.k_pos0;
+        hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
+    }
+    if (hi < lo) hi = lo;
+    return {lo, hi};
 }
 
 template <bool kBf16>
@@ -424,7 +264,7 @@ template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 __global__ void __launch_bounds__(Cfg<D, NQ>::kThreads, NQ == 1 ? 2 : 1)
 fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
-                 const __grid_constant__ FwdArgs a) {
+                 const FwdArgs a) {
     using C = Cfg<D, NQ>;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte-swizzled tiles need a 1024-byte aligned base
@@ -433,22 +273,17 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t sQ = smem_base + C::kSmemQ;
     const uint32_t sK = smem_base + C::kSmemK;
     const uint32_t sV = smem_base + C::kSmemV;
-    const uint32_t sStage = smem_base + C::kSmemStage;
     const uint32_t bar0 = smem_base + C::kSmemBar;
     // barrier map
-    const uint32_t bar_q_full = bar0;                            // [NQ]  Q tile of group i has landed
-    const uint32_t bar_q_empty = bar_q_full + 8 * NQ;            // [NQ]  last Q K^T of group i's item has completed
-    const uint32_t bar_s_full = bar_q_empty + 8 * NQ;            // [NQ]
+    const uint32_t bar_q_full = bar0;
+    const uint32_t bar_s_full = bar0 + 8;                        // [NQ]
     const uint32_t bar_o_full = bar_s_full + 8 * NQ;             // [NQ]
     const uint32_t bar_k_full = bar_o_full + 8 * NQ;             // [kStages]
     const uint32_t bar_k_empty = bar_k_full + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_full = bar_k_empty + 8 * C::kStages;    // [kStages]
     const uint32_t bar_v_empty = bar_v_full + 8 * C::kStages;    // [kStages]
-    const uint32_t bar_item_full = bar_v_empty + 8 * C::kStages;      // [kItemSlots] (persistent kernel)
-    const uint32_t bar_item_empty = bar_item_full + 8 * C::kItemSlots;  // [kItemSlots]
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kSmemBar + 8 * C::kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kSmemBar + 8 * C::kNumBars + 4);
-    volatile uint32_t* item_ring = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kSmemBar + 8 * C::kNumBars + 16);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -456,147 +291,95 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     int tr_n = 0;
     FA_TR(90);
 #endif
-    FA_CTA_TIME(0);
 
     // Programmatic dependent launch: let the next kernel of the stream start its own set-up as
     // soon as SMs free up, and do this kernel's set-up (index arithmetic, barriers, TMEM) before
     // waiting for the kernel in front of it; no global memory is touched before grid_dep_wait().
     grid_dep_launch_dependents();
 
+    // ---- which query tiles does this CTA own ------------------------------------
+    const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
+    // CTA order: groups of unit_group units; inside a group all units' first query block, then
+    // all second ones, ...  With a causal mask the blocks are visited heaviest first, so the
+    // grid is close to a longest-job-first schedule while the K/V working set of the CTAs in
+    // flight (one group) stays far below the L2 size.
+    // (the divisors are launch constants: multiply-high instead of the hardware's slow integer divide,
+    // which sat on the path to the first TMA load)
+    const uint32_t group = fast_div(a.div_group_ctas, blockIdx.x);
+    const int unit0 = static_cast<int>(group) * a.unit_group;
+    const bool full_group = unit0 + a.unit_group <= a.units;
+    const uint32_t rem = blockIdx.x - group * a.div_group_ctas.d;
+    const uint32_t bx = fast_div(full_group ? a.div_gsize : a.div_last_gsize, rem);
+    const int unit = unit0 + static_cast<int>(rem - bx * (full_group ? a.div_gsize.d : a.div_last_gsize.d));
+    const int kv_unit = static_cast<int>(fast_div(a.div_kv_group, static_cast<uint32_t>(unit)));  // grouped-query attention: K/V head of this unit
+    const uint32_t qb_raw = fast_div(a.div_splits, bx);
+    const int split = static_cast<int>(bx - qb_raw * a.div_splits.d);
+    int qb = static_cast<int>(qb_raw);
+    if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
+    FA_TR(94);
+    TileRange range[NQ];
+    int lo = 0x7fffffff, hi = 0;
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+        range[i] = kv_tile_range(a, qb * NQ + i, split);
+        if (range[i].hi > range[i].lo) {
+            lo = min(lo, range[i].lo);
+            hi = max(hi, range[i].hi);
+        }
+    }
+    const int n_union = hi > lo ? hi - lo : 0;  // KV tiles streamed by this CTA: [lo, hi)
+    FA_TR(95);
+
     // ---- set-up ----------------------------------------------------------------
-    // The barriers are initialised by the lanes that use them first: the producer lane its ring
-    // and Q barriers, after which it immediately puts the first item's Q tiles and the first
+    // The producer lane initialises the barriers and immediately puts the Q tiles and the first
     // ring-full of K/V tiles in flight, so that the HBM latency of these first loads overlaps the
     // TMEM allocation and the CTA-wide synchronisation instead of following them.
-    int fail = 0;
-    uint32_t prod_pub = 0;   // items published so far (producer lane)
-    Item<NQ> prod_item;
-    bool prod_have = false;
-    int prod_t = 0;          // KV tiles of prod_item already requested
-    uint32_t prod_g = 0;     // KV tiles requested so far (position in the ring)
-    uint32_t prod_q[NQ];     // Q tiles requested so far, per softmax group
-#pragma unroll
-    for (int i = 0; i < NQ; ++i) prod_q[i] = 0;
-
-    auto load_kv_tile = [&](const Item<NQ>& it, int t, uint32_t g) __attribute__((always_inline)) {
-        const int st = static_cast<int>(g % C::kStages);
-        const int row = (it.hi - 1 - t) * kTile;  // KV tiles are walked from the last to the first
-        mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
-#pragma unroll
-        for (int b = 0; b < C::kBoxes; ++b)
-            tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, it.pos.kv_unit);
-        return st;
-    };
-    auto load_v_tile = [&](const Item<NQ>& it, int t, int st) __attribute__((always_inline)) {
-        const int row = (it.hi - 1 - t) * kTile;
-        mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
-#pragma unroll
-        for (int b = 0; b < C::kBoxes; ++b)
-            tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, it.pos.kv_unit);
-    };
-    auto load_q_tile = [&](const Item<NQ>& it, int i) __attribute__((always_inline)) {
-        mbar_expect_tx(bar_q_full + 8 * i, C::kTileBytes);
-#pragma unroll
-        for (int b = 0; b < C::kBoxes; ++b)
-            tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full + 8 * i, b * 64,
-                        tile_of_group<NQ>(it.pos.qb, i) * kTile, it.pos.unit);
-    };
-
-    // Producer lane: next item of this CTA that streams at least one KV tile.  Every item claimed on
-    // the way (the softmax groups write zero rows for items without KV tiles) and the end of the
-    // list are published to the other roles.
-    auto producer_next = [&]() __attribute__((always_inline)) -> bool {
-        for (;;) {
-            uint32_t pos;
-            if constexpr (C::kPersist) {
-                pos = claim_item(a);
-#ifdef FA_TRACE
-                if (blockIdx.x < 256 && prod_pub < 64) fa_claims[blockIdx.x * 64 + prod_pub] = pos;
-#endif
-                const uint32_t slot = prod_pub % C::kItemSlots;
-                if (prod_pub >= C::kItemSlots &&
-                    !mbar_wait(bar_item_empty + 8 * slot, ((prod_pub / C::kItemSlots) - 1) & 1, abort_flag)) {
-                    fail = 12;
-                    return false;
-                }
-                item_ring[slot] = pos;
-                mbar_arrive(bar_item_full + 8 * slot);  // (release: the store above is visible to whoever sees the phase)
-                ++prod_pub;
-            } else {
-                pos = prod_pub++ == 0 ? blockIdx.x : kNoItem;
-            }
-            if (pos == kNoItem) return false;
-            prod_item = make_item<NQ>(a, pos);
-            if (prod_item.hi > prod_item.lo) return true;
-        }
-    };
-    // The other roles: next published item (warp-collective).
-    auto consume_item = [&](uint32_t& n_seen) __attribute__((always_inline)) -> uint32_t {
-        if constexpr (C::kPersist) {
-            const uint32_t slot = n_seen % C::kItemSlots;
-            if (!mbar_wait_warp(bar_item_full + 8 * slot, (n_seen / C::kItemSlots) & 1, abort_flag)) {
-                fail = 11;
-                return kNoItem;
-            }
-            const uint32_t pos = item_ring[slot];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_item_empty + 8 * slot);
-            ++n_seen;
-            return pos;
-        } else {
-            return n_seen++ == 0 ? blockIdx.x : kNoItem;
-        }
-    };
-    auto consume_streaming_item = [&](uint32_t& n_seen, Item<NQ>* it) __attribute__((always_inline)) -> bool {
-        for (;;) {
-            const uint32_t pos = consume_item(n_seen);
-            if (pos == kNoItem) return false;
-            *it = make_item<NQ>(a, pos);
-            if (it->hi > it->lo) return true;
-        }
-    };
-
+    int prefilled = 0;  // K/V tiles whose loads were issued during set-up (producer lane only)
     if (warp == C::kProducerWarp && lane == 0) {
         *abort_flag = 0;
-        for (int i = 0; i < NQ; ++i) {
-            mbar_init(bar_q_full + 8 * i, 1);
-            mbar_init(bar_q_empty + 8 * i, 1);
-        }
+        mbar_init(bar_q_full, 1);
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(bar_k_full + 8 * s, 1);
             mbar_init(bar_k_empty + 8 * s, 1);
             mbar_init(bar_v_full + 8 * s, 1);
             mbar_init(bar_v_empty + 8 * s, 1);
         }
-        if constexpr (C::kPersist) {
-            for (int s = 0; s < C::kItemSlots; ++s) {
-                mbar_init(bar_item_full + 8 * s, 1);
-                mbar_init(bar_item_empty + 8 * s, C::kItemReaders);
-            }
-        }
         mbar_fence_init();
-        prod_have = producer_next();  // (the claim counter is not data of the kernel in front: no need to wait for it)
         grid_dep_wait();
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
         tma_prefetch_desc(&tmap_v);
         if (a.o_tma) tma_prefetch_desc(&tmap_o);
-        if (prod_have) {
+        if (n_union > 0) {
+            int q_tiles = 0;
+#pragma unroll
+            for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
+            mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
 #pragma unroll
             for (int i = 0; i < NQ; ++i) {
-                if (prod_item.r[i].hi > prod_item.r[i].lo) {
-                    load_q_tile(prod_item, i);
-                    ++prod_q[i];
+                if (range[i].hi > range[i].lo) {
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
+                                    (qb * NQ + i) * kTile, unit);
                 }
             }
-            const int pre = min(C::kStages, prod_item.hi - prod_item.lo);
-            for (; prod_t < pre; ++prod_t, ++prod_g) {  // the ring is empty: no waits
-                const int st = load_kv_tile(prod_item, prod_t, prod_g);
-                load_v_tile(prod_item, prod_t, st);
+            prefilled = min(C::kStages, n_union);
+            for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
+                const int row = (hi - 1 - t) * kTile;  // KV tiles are walked from the last to the first
+                mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
+#pragma unroll
+                for (int b = 0; b < C::kBoxes; ++b)
+                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, kv_unit);
+                mbar_expect_tx(bar_v_full + 8 * t, C::kTileBytes);
+#pragma unroll
+                for (int b = 0; b < C::kBoxes; ++b)
+                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, kv_unit);
             }
         }
     }
     if (warp == C::kMmaWarp) {
+        // (the barriers the producer lane does not need for its first loads are initialised here, off its path)
         if (lane == 0) {
             for (int i = 0; i < NQ; ++i) {
                 mbar_init(bar_s_full + 8 * i, 1);
@@ -605,61 +388,48 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_fence_init();
         }
         __syncwarp();
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
-        tmem_relinquish();
+        if (n_union > 0) {
+            tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
+            tmem_relinquish();
+        }
     }
     grid_dep_wait();  // every thread, before its first global access (the producer lane has passed it already)
-    FA_CTA_TIME(1);
     FA_TR(92);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     FA_TR(93);
-    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_base = (n_union > 0) ? *tmem_slot : 0u;
+
+    int fail = 0;
 
     // The helper warpgroup (producer, MMA issuer, two idle warps) hands most of its registers to
     // the softmax warpgroups, which hold a 128-column score row per thread.  Each register
     // regime covers one whole branch below.
     if (warp >= NQ * 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsHelper));
-        if (warp == C::kProducerWarp) {
+        if (n_union > 0 && warp == C::kProducerWarp) {
             // ======================= TMA producer ===================================
             if (lane == 0) {
-                bool q_owed = false;  // the Q tiles of prod_item have not been requested yet
-                while (prod_have && fail == 0) {
-                    const int n_union = prod_item.hi - prod_item.lo;
-                    for (; prod_t < n_union; ++prod_t, ++prod_g) {
-                        const int st = static_cast<int>(prod_g % C::kStages);
-                        const uint32_t ph = (prod_g / C::kStages) & 1;
-                        if (prod_g >= C::kStages && !mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
-                        FA_TR(10);
-                        load_kv_tile(prod_item, prod_t, prod_g);
-                        if (q_owed) {
-                            // A new item: its first K tile is in flight (its ring slot came free long ago); the
-                            // Q buffer of a group is free once its last Q K^T of the previous item has completed.
-                            q_owed = false;
+                for (int t = prefilled; t < n_union; ++t) {
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int row = (hi - 1 - t) * kTile;
+                    if (!mbar_wait(bar_k_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 1; break; }
+                    FA_TR(10);
+                    mbar_expect_tx(bar_k_full + 8 * st, C::kTileBytes);
 #pragma unroll
-                            for (int i = 0; i < NQ; ++i) {
-                                if (prod_item.r[i].hi > prod_item.r[i].lo) {
-                                    if (prod_q[i] > 0 && !mbar_wait(bar_q_empty + 8 * i, (prod_q[i] - 1) & 1, abort_flag)) { fail = 10; break; }
-                                    FA_TR(12);
-                                    load_q_tile(prod_item, i);
-                                    ++prod_q[i];
-                                }
-                            }
-                            if (fail != 0) break;
-                        }
-                        if (prod_g >= C::kStages && !mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
-                        FA_TR(11);
-                        load_v_tile(prod_item, prod_t, st);
-                    }
-                    if (fail != 0) break;
-                    prod_have = producer_next();
-                    prod_t = 0;
-                    q_owed = true;
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sK + st * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * st, b * 64, row, kv_unit);
+                    if (!mbar_wait(bar_v_empty + 8 * st, ph ^ 1, abort_flag)) { fail = 2; break; }
+                    FA_TR(11);
+                    mbar_expect_tx(bar_v_full + 8 * st, C::kTileBytes);
+#pragma unroll
+                    for (int b = 0; b < C::kBoxes; ++b)
+                        tma_load_3d(sV + st * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * st, b * 64, row, kv_unit);
                 }
             }
-        } else if (warp == C::kMmaWarp) {
+        } else if (n_union > 0 && warp == C::kMmaWarp) {
             // ======================= MMA issuer =====================================
             // The warp walks the loop together (it meets the softmax warpgroups at named
             // barriers); one elected lane issues the MMAs and commits.
@@ -674,178 +444,113 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const uint32_t q_lo = static_cast<uint32_t>(dqk) | (sQ >> 4);
             const uint32_t k_lo = static_cast<uint32_t>(dqk) | (sK >> 4);
             const uint32_t v_lo = static_cast<uint32_t>(dvv) | (sV >> 4);
-            auto issue_pv_a = [&](int i, int st, uint32_t accumulate) __attribute__((always_inline)) {
+            auto issue_qk = [&](int i, int st) {
+                issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
+                                  k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
+            };
+            auto issue_pv_a = [&](int i, int st, uint32_t accumulate) {
                 issue_pv_first(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
                                v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv, accumulate);
             };
-            auto issue_pv_b = [&](int i, int st) __attribute__((always_inline)) {
+            auto issue_pv_b = [&](int i, int st) {
                 issue_pv_rest(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
                               v_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_pv);
             };
-            auto active = [&](const TileRange& rg, int tile) __attribute__((always_inline)) { return tile >= rg.lo && tile < rg.hi; };
-            // S_i = Q_i K^T for KV tile `tile` of a query tile with KV range rg, K in ring slot st; the
-            // last Q K^T of an item also releases the group's Q buffer
-            auto issue_qk = [&](const TileRange& rg, int i, int tile, int st) __attribute__((always_inline)) {
-                if (leader) {
-                    issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
-                                      k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
-                    umma_commit(bar_s_full + 8 * i);
-                    if (C::kPersist && tile == rg.lo) umma_commit(bar_q_empty + 8 * i);
-                }
-            };
-            uint32_t items_seen = 0;
-            Item<NQ> cur, nxt;
-            bool have = consume_streaming_item(items_seen, &cur);
-            uint32_t g = 0;       // KV tiles consumed so far (position in the ring)
-            uint32_t q_seen[NQ];  // Q tiles consumed so far, per softmax group
-#pragma unroll
-            for (int i = 0; i < NQ; ++i) q_seen[i] = 0;
+            auto active = [&](int i, int tile) { return tile >= range[i].lo && tile < range[i].hi; };
             do {
-                if (!have) break;
-                // first Q K^T of the first item
-#pragma unroll
-                for (int i = 0; i < NQ; ++i) {
-                    if (cur.r[i].hi > cur.r[i].lo) {
-                        if (!mbar_wait_warp(bar_q_full + 8 * i, 0, abort_flag)) { fail = 3; break; }
-                        ++q_seen[i];
-                    }
-                }
-                if (fail != 0) break;
+                if (!mbar_wait_warp(bar_q_full, 0, abort_flag)) { fail = 3; break; }
                 if (!mbar_wait_warp(bar_k_full, 0, abort_flag)) { fail = 4; break; }
                 FA_TR(26);
                 tc_fence_after_sync();
+                if (leader) {
 #pragma unroll
-                for (int i = 0; i < NQ; ++i)
-                    if (active(cur.r[i], cur.hi - 1)) issue_qk(cur.r[i], i, cur.hi - 1, 0);
-                if (leader) umma_commit(bar_k_empty);
-                while (have && fail == 0) {
-                    bool have_next = false;
-                    const int n_union = cur.hi - cur.lo;
-                    for (int t = 0; t < n_union && fail == 0; ++t, ++g) {
-                        // the item after this one is asked for when its first tile comes into view; the
-                        // producer has published it by then (it did so after this item's last load)
-                        if (t + 1 == n_union) {
-                            have_next = consume_streaming_item(items_seen, &nxt);
-                            if (fail != 0) break;
-                        }
-                        const int tile = cur.hi - 1 - t;
-                        const int st = static_cast<int>(g % C::kStages);
-                        const uint32_t ph = (g / C::kStages) & 1;
-                        const int st1 = static_cast<int>((g + 1) % C::kStages);
-                        const uint32_t ph1 = ((g + 1) / C::kStages) & 1;
-                        const bool last = t + 1 == n_union;
-                        const bool more = !last || have_next;  // another KV tile follows in the stream
-                        const int ntile = last ? nxt.hi - 1 : tile - 1;
-                        TileRange nr[NQ];  // KV ranges of the query tiles of that tile's item
-#pragma unroll
-                        for (int i = 0; i < NQ; ++i) {
-                            nr[i].lo = last ? nxt.r[i].lo : cur.r[i].lo;
-                            nr[i].hi = last ? nxt.r[i].hi : cur.r[i].hi;
-                        }
-                        // Operands of the next tile's Q K^T: its K tile and, when it opens the next item, that
-                        // item's Q tiles.  At an item boundary they may still be in flight, and this step's
-                        // P V must not wait for them: they are then looked at when the first such Q K^T is due.
-                        // Groups that sit this tile out but take the next one get their Q K^T at that moment too.
-                        bool next_ready = !more;
-                        auto next_operands = [&]() __attribute__((always_inline)) {
-                            if (next_ready || fail != 0) return;
-                            if (!mbar_wait_warp(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; return; }
-                            if (last) {
-#pragma unroll
-                                for (int i = 0; i < NQ; ++i) {
-                                    if (nxt.r[i].hi > nxt.r[i].lo) {
-                                        if (!mbar_wait_warp(bar_q_full + 8 * i, q_seen[i] & 1, abort_flag)) { fail = 5; return; }
-                                        ++q_seen[i];
-                                    }
-                                }
-                            }
-                            FA_TR(23);
-                            next_ready = true;
-                            tc_fence_after_sync();
-#pragma unroll
-                            for (int i = 0; i < NQ; ++i)
-                                if (!active(cur.r[i], tile) && active(nr[i], ntile)) issue_qk(nr[i], i, ntile, st1);
-                        };
-                        // the P V of this step needs V
-                        if (!mbar_wait_warp(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
-                        FA_TR(20);
-                        if (more) {
-                            // Inside an item the next K tile landed long ago: its barrier is looked at now, while
-                            // the warp would wait for P anyway (a poll costs hundreds of cycles while the tensor
-                            // pipe streams operands, and between P V and Q K^T it would sit on the critical
-                            // chain).  The same goes for a group that sits this tile out and takes the next.
-                            bool idle_takes_next = false;
-#pragma unroll
-                            for (int i = 0; i < NQ; ++i) idle_takes_next |= !active(cur.r[i], tile) && active(nr[i], ntile);
-                            if (!last || idle_takes_next) next_operands();
-                            if (fail != 0) break;
-                        }
-#pragma unroll
-                        for (int i = 0; i < NQ; ++i) {
-                            if (active(cur.r[i], tile)) {
-                                // P V starts on the first three quarters of P while the last is exponentiated
-                                named_sync(1 + 2 * i);
-                                FA_TR(21 + 10 * i);
-                                tc_fence_after_sync();
-                                if (leader) issue_pv_a(i, st, tile < cur.r[i].hi - 1 ? 1u : 0u);
-                                named_sync(2 + 2 * i);
-                                tc_fence_after_sync();
-                                if (leader) {
-                                    issue_pv_b(i, st);
-                                    if (tile == cur.r[i].lo) umma_commit(bar_o_full + 8 * i);
-                                }
-                                FA_TR(22 + 10 * i);
-                                if (more && active(nr[i], ntile)) {
-                                    next_operands();
-                                    if (fail != 0) break;
-                                    issue_qk(nr[i], i, ntile, st1);
-                                    FA_TR(24 + 10 * i);
-                                }
-                            }
-                        }
-                        next_operands();  // (nobody took the next tile yet: its operands are still owed a look)
-                        if (fail != 0) break;
-                        if (leader) {
-                            umma_commit(bar_v_empty + 8 * st);
-                            if (more) umma_commit(bar_k_empty + 8 * st1);
+                    for (int i = 0; i < NQ; ++i) {
+                        if (active(i, hi - 1)) {
+                            issue_qk(i, 0);
+                            umma_commit(bar_s_full + 8 * i);
                         }
                     }
-                    cur = nxt;
-                    have = have_next;
+                    umma_commit(bar_k_empty);
+                }
+                for (int t = 0; t < n_union && fail == 0; ++t) {
+                    const int tile = hi - 1 - t;
+                    const int st = t % C::kStages;
+                    const uint32_t ph = (t / C::kStages) & 1;
+                    const int st1 = (t + 1) % C::kStages;
+                    const uint32_t ph1 = ((t + 1) / C::kStages) & 1;
+                    const bool more = t + 1 < n_union;
+                    // K/V tiles arrive long before they are needed; their barriers are looked at now,
+                    // while the warp would wait for P anyway
+                    if (!mbar_wait_warp(bar_v_full + 8 * st, ph, abort_flag)) { fail = 6; break; }
+                    FA_TR(20);
+                    if (more) {
+                        if (!mbar_wait_warp(bar_k_full + 8 * st1, ph1, abort_flag)) { fail = 7; break; }
+                        FA_TR(23);
+                    }
+#pragma unroll
+                    for (int i = 0; i < NQ; ++i) {
+                        if (active(i, tile)) {
+                            // P V starts on the first three quarters of P while the last is exponentiated
+                            named_sync(1 + 2 * i);
+                            FA_TR(21 + 10 * i);
+                            tc_fence_after_sync();
+                            if (leader) issue_pv_a(i, st, tile < range[i].hi - 1 ? 1u : 0u);
+                            named_sync(2 + 2 * i);
+                            tc_fence_after_sync();
+                            if (leader) {
+                                issue_pv_b(i, st);
+                                if (tile == range[i].lo) umma_commit(bar_o_full + 8 * i);
+                            }
+                            FA_TR(22 + 10 * i);
+                        }
+                        if (more && active(i, tile - 1)) {
+                            if (leader) {
+                                issue_qk(i, st1);
+                                umma_commit(bar_s_full + 8 * i);
+                            }
+                            FA_TR(24 + 10 * i);
+                        }
+                    }
+                    if (leader) {
+                        umma_commit(bar_v_empty + 8 * st);
+                        if (more) umma_commit(bar_k_empty + 8 * st1);
+                    }
                 }
             } while (false);
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
         // ======================= softmax / epilogue =============================
-        const int qi = warp >> 2;                        // which softmax group of the CTA
+        const int qi = warp >> 2;                        // which query tile of the CTA
+        const int rb = qb * NQ + qi;                     // its 128-row block inside the unit
         const int r = threadIdx.x & 127;                 // row inside the tile
+        const int row = rb * kTile + r;                  // row inside the unit
+        const long long qpos = a.q_pos0 + row;
+        const TileRange mine_r = (qi == 0) ? range[0] : range[NQ - 1];
+        const int t_lo = mine_r.lo;
+        const int n_tiles = mine_r.hi - mine_r.lo;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tmem_s = tmem_base + qi * kTile;          // S accumulator, 128 fp32 columns
         const uint32_t tmem_p = tmem_s;                          // P (16-bit, two per column) over S[0,64)
         const uint32_t tmem_o = tmem_base + C::kTmemO + qi * D;  // O accumulator, D fp32 columns
         const uint32_t my_s_full = bar_s_full + 8 * qi;
         const uint32_t my_o_full = bar_o_full + 8 * qi;
+        float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
+        float l_sum = 0.0f;
+        float slope2 = 0.0f;
+        if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
         // every unmasked key lies at or before the query: |q - k| = q - k
         const bool keys_not_after = a.is_causal || a.window_right == 0;
+        unsigned long long subseq = 0;
+        if constexpr (kDropout)
+            subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
+                     static_cast<unsigned long long>(rb * a.num_splits + split);
         const float scale2 = a.scale_log2;
-        uint32_t s_seen = 0;   // S tiles consumed so far by this group (phase of s_full)
-        uint32_t o_seen = 0;   // items with at least one KV tile finished so far (phase of o_full)
-        bool staged = false;   // a TMA store of this warp may still be reading its staging buffer
-
-        // One item of this softmax group.  The next item is looked up (position, KV range, ALiBi slope,
-        // first dropout bits) while the group waits for the last P V of the current one.
-        struct GroupItem {
-            int unit, split, rb, t_lo, n_tiles;
-            float slope2;
-            unsigned long long subseq;
-            uint32_t keep_first;
-        };
-        // Dropout keep bits of a row for KV tile j (counted from the first KV tile of the query tile):
-        // bit 2*g + w <-> columns 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each
-        // (lane = 2*i + row-half: draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its
-        // half.  Computed one tile ahead, while the warp would otherwise wait for S.
-        auto tile_keep_bits = [&](unsigned long long subseq, int j) __attribute__((always_inline)) -> uint32_t {
+        // Dropout keep bits of this row for KV tile j of this query tile: bit 2*g + w <-> columns
+        // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
+        // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
+        // tile ahead, while the warp would otherwise wait for S.
+        auto tile_keep_bits = [&](int j) -> uint32_t {
             if constexpr (!kDropout) return 0xffffffffu;
             uint32_t mine = 0;
             if (lane < 16) mine = philox_keep4(a.drop, subseq, 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
@@ -855,48 +560,9 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
             return bits;
         };
-        uint32_t items_seen = 0;
-        auto fetch_item = [&](GroupItem* it) __attribute__((always_inline)) -> bool {
-            for (;;) {
-                const uint32_t pos = consume_item(items_seen);
-                if (pos == kNoItem) return false;
-                FA_TR(100000 + static_cast<long long>(pos));
-                const ItemPos ip = item_position<NQ>(a, pos);
-                const int rb = tile_of_group<NQ>(ip.qb, qi);  // this group's 128-row block inside the unit
-                if (rb >= a.tr) continue;                     // the unit has an odd number of query tiles
-                const TileRange rg = kv_tile_range(a, rb, ip.split);
-                it->unit = ip.unit;
-                it->split = ip.split;
-                it->rb = rb;
-                it->t_lo = rg.lo;
-                it->n_tiles = rg.hi - rg.lo;
-                it->slope2 = 0.0f;
-                if constexpr (kAlibi) it->slope2 = a.alibi_slopes[ip.unit % a.heads] * kLog2e;
-                it->subseq = 0;
-                if constexpr (kDropout)
-                    it->subseq = (a.drop.unit0 + ip.unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
-                                 static_cast<unsigned long long>(rb * a.num_splits + ip.split);
-                it->keep_first = it->n_tiles > 0 ? tile_keep_bits(it->subseq, it->n_tiles - 1) : 0u;
-                return true;
-            }
-        };
-        GroupItem item;
-        bool have_item = fetch_item(&item);
-        while (have_item) {
-        const int unit = item.unit;
-        const int split = item.split;
-        const int rb = item.rb;
-        const int row = rb * kTile + r;                  // row inside the unit
-        const long long qpos = a.q_pos0 + row;
-        const int t_lo = item.t_lo;
-        const int n_tiles = item.n_tiles;
-        const float slope2 = item.slope2;
-        const unsigned long long subseq = item.subseq;
-        float m_ref = -INFINITY;  // running max in log2 units (scaled, biased)
-        float l_sum = 0.0f;
-        uint32_t keep_next = item.keep_first;
+        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(n_tiles - 1) : 0u;  // argument: tile index from the first KV tile
 
-        for (int j = 0; j < n_tiles; ++j, ++s_seen) {
+        for (int j = 0; j < n_tiles; ++j) {
             const int cb = t_lo + n_tiles - 1 - j;  // from the last KV tile of this query tile to the first
             const long long kbase = a.k_pos0 + static_cast<long long>(cb) * kTile;
             // columns this row may attend to inside the tile: [c_lo, c_hi] (worked out before S arrives)
@@ -906,7 +572,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
             const bool tile_masked_pre = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
             FA_TR(1);
-            if (fail != 0 || !mbar_wait_warp(my_s_full, s_seen & 1, abort_flag)) {
+            if (fail != 0 || !mbar_wait_warp(my_s_full, j & 1, abort_flag)) {
                 // a wait gave up: keep the barrier protocol alive (the MMA warp counts on two
                 // arrivals per tile from every softmax thread) and do nothing else
                 fail = 8;
@@ -930,17 +596,9 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
             const bool tile_masked = tile_masked_pre;
             if (tile_masked) {
-                // (two passes: a causal diagonal, the common case, needs only the upper bound)
-                if (__any_sync(0xffffffffu, c_hi < kTile - 1)) {
 #pragma unroll
-                    for (int c = 0; c < 128; ++c)
-                        if (c > c_hi) s[c] = -INFINITY;
-                }
-                if (__any_sync(0xffffffffu, c_lo > 0)) {
-#pragma unroll
-                    for (int c = 0; c < 128; ++c)
-                        if (c < c_lo) s[c] = -INFINITY;
-                }
+                for (int c = 0; c < 128; ++c)
+                    if (c < c_lo || c > c_hi) s[c] = -INFINITY;
             }
 
             // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
@@ -1056,6 +714,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         tc_fence_before_sync();
                         named_arrive(1 + 2 * qi);
                         FA_TR(8);
+                        FA_TR(8);
                     }
                 }
             };
@@ -1067,22 +726,16 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_before_sync();
             named_arrive(2 + 2 * qi);
             FA_TR(7);
-            if (j + 1 < n_tiles) keep_next = tile_keep_bits(subseq, n_tiles - 2 - j);
+            if (j + 1 < n_tiles) keep_next = tile_keep_bits(n_tiles - 2 - j);
         }
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
         FA_TR(91);
-        GroupItem next_item_;
-        const bool have_next_item = fetch_item(&next_item_);
         bool have_o = false;
-        if (n_tiles > 0) {
-            if (fail == 0) {
-                if (mbar_wait_warp(my_o_full, o_seen & 1, abort_flag)) { tc_fence_after_sync(); have_o = true; }
-                else fail = 9;
-            }
-            ++o_seen;
+        if (n_tiles > 0 && fail == 0) {
+            if (mbar_wait_warp(my_o_full, 0, abort_flag)) { tc_fence_after_sync(); have_o = true; }
+            else fail = 9;
         }
-        if (fail == 0) {  // (after a failed wait the results are void; the items are still walked for the barrier protocol)
         FA_TR(96);
         float inv = 0.0f;
         if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
@@ -1095,63 +748,41 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         } else if (a.lse != nullptr && row_ok) {
             a.lse[unit_ll * a.seqlen_q + row] = lse_val;
         }
-        if (a.o_tma) {
-            // 16-bit output of an unsplit launch: each warp packs its 32 rows, one 64-column box at a
-            // time, into shared memory in the 128-byte-swizzled box layout and hands them to the TMA
-            // unit, which writes whole lines and clips rows >= seqlen_q and columns >= head_dim.
-            // One CTA per item: the boxes are staged in the query tile's own Q buffer (free once the
-            // last Q K^T has completed, which o_full implies).  Persistent kernel: in the warp's own
-            // 4 KB, reused box after box, because the Q buffer is already being refilled.
+        if (a.o_tma && have_o) {
+            // 16-bit output of an unsplit launch: the rows are staged in this query tile's Q buffer
+            // (free once the last Q K^T has completed, which o_full implies) in the 128-byte-swizzled
+            // box layout, and each warp hands its 32 rows to the TMA unit, which writes whole lines
+            // and clips rows >= seqlen_q and columns >= head_dim.
+            const uint32_t stage = sQ + qi * C::kTileBytes;
             const int y0 = rb * kTile + (warp & 3) * 32;
 #pragma unroll
-            for (int b = 0; b < C::kBoxes; ++b) {
+            for (int b = 0; b < C::kBoxes; ++b) {  // a 64-column box at a time: its store runs while the next is packed
                 uint32_t orow[2][32];
-                if (have_o) {
-                    tmem_ld32(tmem_o + lane_base + b * 64, orow[0]);
-                    tmem_ld32(tmem_o + lane_base + b * 64 + 32, orow[1]);
-                    tmem_wait_ld();
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) orow[0][i] = orow[1][i] = 0u;
-                }
-                uint32_t packed[2][16];
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        packed[h][i >> 1] = pack2<kBf16>(__uint_as_float(orow[h][i]) * inv, __uint_as_float(orow[h][i + 1]) * inv);
-                uint32_t box;
-                if constexpr (C::kPersist) {
-                    box = sStage + warp * 4096;
-                    if (staged) {  // the previous box of this warp must have left the buffer
-                        if (lane == 0) tma_store_wait_read();
-                        __syncwarp();
-                    }
-                } else {
-                    box = sQ + qi * C::kTileBytes + b * (kTile * 128) + (warp & 3) * (32 * 128);
-                }
-                const uint32_t row_addr = box + lane * 128;
+                tmem_ld32(tmem_o + lane_base + b * 64, orow[0]);
+                tmem_ld32(tmem_o + lane_base + b * 64 + 32, orow[1]);
+                tmem_wait_ld();
+                const uint32_t row_addr = stage + b * (kTile * 128) + r * 128;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t chunk = static_cast<uint32_t>(h * 4 + i) ^ static_cast<uint32_t>(lane & 7);
-                        st_shared_v4(row_addr + chunk * 16, packed[h][4 * i], packed[h][4 * i + 1], packed[h][4 * i + 2],
-                                     packed[h][4 * i + 3]);
+                    for (int i = 0; i < 32; i += 8) {
+                        const uint32_t x = pack2<kBf16>(__uint_as_float(orow[h][i]) * inv, __uint_as_float(orow[h][i + 1]) * inv);
+                        const uint32_t y = pack2<kBf16>(__uint_as_float(orow[h][i + 2]) * inv, __uint_as_float(orow[h][i + 3]) * inv);
+                        const uint32_t z = pack2<kBf16>(__uint_as_float(orow[h][i + 4]) * inv, __uint_as_float(orow[h][i + 5]) * inv);
+                        const uint32_t w = pack2<kBf16>(__uint_as_float(orow[h][i + 6]) * inv, __uint_as_float(orow[h][i + 7]) * inv);
+                        const uint32_t chunk = static_cast<uint32_t>(h * 4 + (i >> 3)) ^ static_cast<uint32_t>(r & 7);
+                        st_shared_v4(row_addr + chunk * 16, x, y, z, w);
                     }
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0 && y0 < a.seqlen_q && b * 64 < a.head_dim) {
-                    tma_store_3d(&tmap_o, box, b * 64, y0, unit);
+                    tma_store_3d(&tmap_o, stage + b * (kTile * 128) + (warp & 3) * (32 * 128), b * 64, y0, unit);
                     tma_store_commit();
                 }
-                staged = true;
             }
             FA_TR(97);
-            if constexpr (!C::kPersist) {
-                if (lane == 0) tma_store_wait_read();
-            }
+            if (lane == 0) tma_store_wait_read();
         } else {
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -1193,12 +824,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
         }
         }
-        }
-        item = next_item_;
-        have_item = have_next_item;
-        }  // items
-        // the staging buffers must outlive the reads of the last TMA stores
-        if (C::kPersist && staged && lane == 0) tma_store_wait_read();
     }
 
     // ---- teardown ------------------------------------------------------------------
@@ -1210,25 +835,19 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         while (clock64() - t0 < 200000) { }
     }
     FA_TR(98);
-    FA_CTA_TIME(2);
     tc_fence_before_sync();
     __syncthreads();
     FA_TR(99);
-    FA_CTA_TIME(3);
-    if (warp == C::kMmaWarp) {
+    if (warp == C::kMmaWarp && n_union > 0) {
         __syncwarp();
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
 }
 
-// ------------------------------------------------------------------ host side
-
-std::atomic<uint32_t> g_launches{0};  // persistent launches so far in this process (all kernel variants)
-
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 cudaError_t launch_one(FwdArgs a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                       const CUtensorMap& to, int units, int sms, cudaStream_t stream) {
+                       const CUtensorMap& to, int units, cudaStream_t stream) {
     auto kern = fwd_tiled_kernel<D, NQ, kBf16, kAlibi, kDropout>;
     constexpr int smem = Cfg<D, NQ>::kSmemBytes;
     static std::atomic<bool> configured[64];
@@ -1241,17 +860,18 @@ cudaError_t launch_one(FwdArgs a, const CUtensorMap& tq, const CUtensorMap& tk, 
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     const int trq = (a.tr + NQ - 1) / NQ;
-    const int per_unit = trq * a.num_splits;
-    const long long items = static_cast<long long>(units) * per_unit;
-    if (items <= 0 || items > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-    a.n_items = static_cast<int>(items);
-    a.div_group_items = make_fastdiv(static_cast<uint32_t>(std::min<long long>(static_cast<long long>(a.unit_group) * per_unit, 0x7fffffffLL)));
+    const long long per_unit = static_cast<long long>(trq) * a.num_splits;
+    const long long ctas = static_cast<long long>(units) * per_unit;
+    if (ctas <= 0 || ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    a.div_group_ctas = make_fastdiv(static_cast<uint32_t>(std::min<long long>(a.unit_group * per_unit, 0x7fffffffLL)));
     a.div_gsize = make_fastdiv(static_cast<uint32_t>(a.unit_group));
     a.div_last_gsize = make_fastdiv(static_cast<uint32_t>(units % a.unit_group == 0 ? a.unit_group : units % a.unit_group));
     a.div_splits = make_fastdiv(static_cast<uint32_t>(a.num_splits));
+    a.div_kv_group = make_fastdiv(static_cast<uint32_t>(a.kv_group));
     // launched with programmatic stream serialization: the kernel may begin its set-up while the
     // kernel before it in the stream drains
     cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(ctas));
     cfg.blockDim = dim3(Cfg<D, NQ>::kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -1260,54 +880,43 @@ cudaError_t launch_one(FwdArgs a, const CUtensorMap& tq, const CUtensorMap& tk, 
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if constexpr (NQ == 2) {
-        // persistent: one CTA per SM; the claim counter of this launch (tag 0 is never issued)
-        uint32_t tag = g_launches.fetch_add(1, std::memory_order_relaxed) + 1;
-        if (tag == 0) tag = g_launches.fetch_add(1, std::memory_order_relaxed) + 1;
-        a.sched_tag = tag;
-        a.sched_slot = static_cast<int>(tag % kSchedSlots);
-        cfg.gridDim = dim3(static_cast<unsigned>(std::min<long long>(items, std::max(1, sms))));
-    } else {
-        cfg.gridDim = dim3(static_cast<unsigned>(items));
-    }
     return cudaLaunchKernelEx(&cfg, kern, tq, tk, tv, to, a);
 }
 
 template <int D, int NQ, bool kBf16>
 cudaError_t launch_flags(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& to, int units, bool alibi, bool dropout, int sms, cudaStream_t stream) {
+                         const CUtensorMap& to, int units, bool alibi, bool dropout, cudaStream_t stream) {
     if (alibi) {
-        return dropout ? launch_one<D, NQ, kBf16, true, true>(a, tq, tk, tv, to, units, sms, stream)
-                       : launch_one<D, NQ, kBf16, true, false>(a, tq, tk, tv, to, units, sms, stream);
+        return dropout ? launch_one<D, NQ, kBf16, true, true>(a, tq, tk, tv, to, units, stream)
+                       : launch_one<D, NQ, kBf16, true, false>(a, tq, tk, tv, to, units, stream);
     }
-    return dropout ? launch_one<D, NQ, kBf16, false, true>(a, tq, tk, tv, to, units, sms, stream)
-                   : launch_one<D, NQ, kBf16, false, false>(a, tq, tk, tv, to, units, sms, stream);
+    return dropout ? launch_one<D, NQ, kBf16, false, true>(a, tq, tk, tv, to, units, stream)
+                   : launch_one<D, NQ, kBf16, false, false>(a, tq, tk, tv, to, units, stream);
 }
 
 template <int D, int NQ>
 cudaError_t launch_dtype(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                         const CUtensorMap& to, int units, bool bf16, bool alibi, bool dropout, int sms,
-                         cudaStream_t stream) {
-    return bf16 ? launch_flags<D, NQ, true>(a, tq, tk, tv, to, units, alibi, dropout, sms, stream)
-                : launch_flags<D, NQ, false>(a, tq, tk, tv, to, units, alibi, dropout, sms, stream);
+                         const CUtensorMap& to, int units, bool bf16, bool alibi, bool dropout, cudaStream_t stream) {
+    return bf16 ? launch_flags<D, NQ, true>(a, tq, tk, tv, to, units, alibi, dropout, stream)
+                : launch_flags<D, NQ, false>(a, tq, tk, tv, to, units, alibi, dropout, stream);
 }
 
 }  // namespace
 
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                             const CUtensorMap& to, int units, bool bf16, bool dropout, int sms, cudaStream_t stream) {
+                             const CUtensorMap& to, int units, bool bf16, bool dropout, cudaStream_t stream) {
     const bool alibi = a.alibi_slopes != nullptr;
-    // two query tiles per item once a unit has more than two (or two without a causal mask); smaller
-    // units keep two independent CTAs per SM instead
+    // two query tiles per CTA once a unit has more than one; a single tile (decode-like
+    // shapes) keeps two independent CTAs per SM instead
     // (with two query tiles and a causal mask the pair would spend half its time on the diagonal tile that
     // only one of them can use: 277 against 308 TFLOP/s at [128,16,256,128])
     const bool pair = a.tr > 2 || (a.tr == 2 && !a.is_causal);
     if (a.head_dim <= 64) {
-        return pair ? launch_dtype<64, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, sms, stream)
-                    : launch_dtype<64, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, sms, stream);
+        return pair ? launch_dtype<64, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream)
+                    : launch_dtype<64, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream);
     }
-    return pair ? launch_dtype<128, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, sms, stream)
-                : launch_dtype<128, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, sms, stream);
+    return pair ? launch_dtype<128, 2>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream)
+                : launch_dtype<128, 1>(a, tq, tk, tv, to, units, bf16, alibi, dropout, stream);
 }
 
 }  // namespace fa

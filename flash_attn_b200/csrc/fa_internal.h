@@ -42,18 +42,15 @@ struct FwdArgs {
     long long q_pos0, k_pos0;
     int o_is_fp32;
     int o_tma;              // O leaves through the TMA store map (16-bit output, unsplit launch)
-    // launch order of the work items (filled by launch_fwd_tiled)
-    int n_items;            // units * query blocks * splits
-    int sched_slot;         // persistent kernel: which claim counter this launch uses, and
-    uint32_t sched_tag;     // the tag that marks the counter as this launch's
-    FastDiv div_group_items, div_gsize, div_last_gsize, div_splits;
+    // launch order of the CTAs (filled by launch_fwd_tiled): divisors of the block index
+    FastDiv div_group_ctas, div_gsize, div_last_gsize, div_splits, div_kv_group;
     DropoutParams drop;
 };
 
 // Launchers implemented in the .cu files; all return a cudaError_t.  `to` is the store map of O
 // (32-row boxes); it is read only when a.o_tma is set.
 cudaError_t launch_fwd_tiled(const FwdArgs& a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
-                             const CUtensorMap& to, int units, bool bf16, bool dropout, int sms, cudaStream_t stream);
+                             const CUtensorMap& to, int units, bool bf16, bool dropout, cudaStream_t stream);
 
 // Device-side argument block of the decode kernel (seqlen_q = 1).
 struct DecodeArgs {
