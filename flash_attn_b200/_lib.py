@@ -10,6 +10,7 @@ LIB_PATH = os.path.join(PKG, "libfa_b200.so")
 
 FA_DTYPE_FP16, FA_DTYPE_BF16, FA_DTYPE_FP32 = 0, 1, 2
 FA_OK = 0
+FA_ACCUM_FIRST, FA_ACCUM_FINAL = 1, 2
 
 #: every symbol include/fa_b200.h declares
 EXPORTS = ["fa_fwd", "fa_fwd_workspace_bytes", "fa_fwd_resolve_splits", "fa_num_splits_heuristic",
@@ -38,6 +39,7 @@ class FwdParams(ctypes.Structure):
         ("status", ctypes.c_void_p),
         ("stream", ctypes.c_void_p),
         ("heads_k", ctypes.c_int),
+        ("accum_o", ctypes.c_void_p), ("accum_lse", ctypes.c_void_p), ("accum_flags", ctypes.c_int),
     ]
 
 

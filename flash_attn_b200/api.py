@@ -45,7 +45,8 @@ def _params(q, k, v, o, lse, softmax_scale, causal, window, alibi_slopes, p_drop
 
 def flash_attn_forward(q, k, v, softmax_scale=None, causal=False, window=(-1, -1), alibi_slopes=None,
                        p_dropout=0.0, seed=0, offset=0, num_splits=1, out=None, out_dtype=None, return_lse=True,
-                       q_pos0=0, k_pos0=0, unit0=0, workspace=None, status=None):
+                       q_pos0=0, k_pos0=0, unit0=0, workspace=None, status=None, accum=None, accum_first=False,
+                       accum_final=False):
     """O, LSE = attention(Q, K, V) on the current CUDA device and stream.
 
     q [B,H,Nq,d], k/v [B,Hk,Nk,d] (Hk divides H; query head h reads K/V head
@@ -53,18 +54,36 @@ def flash_attn_forward(q, k, v, softmax_scale=None, causal=False, window=(-1, -1
     right) with -1 = unbounded; `alibi_slopes` fp32 [H]; `num_splits` 0 = the
     reference heuristic, 1 = none, n = forced; `q_pos0`/`k_pos0` = global positions
     of row/column 0 (for one block of a sharded sequence).  Returns (o, lse).
+
+    `accum` = (o_acc fp32 [B,H,Nq,d], lse_acc fp32 [B,H,Nq]): the launch merges its
+    result into this running pair in its epilogue (key blocks that arrive one launch
+    at a time); `accum_first` marks the first block (the pair is only written),
+    `accum_final` the last one, and only that call writes and returns (o, lse) --
+    the others return (None, None).
     """
     L = _lib.load()
     if not q.is_cuda:
         raise ValueError("flash_attn_forward needs CUDA tensors (use flash_attn_forward_host for host buffers)")
     B, H, Nq, d = q.shape
-    if out is None:
+    writes_output = accum is None or accum_final
+    if out is None and writes_output:
         out = torch.empty((B, H, Nq, d), device=q.device, dtype=out_dtype or q.dtype)
-    lse = torch.empty((B, H, Nq), device=q.device, dtype=torch.float32) if return_lse else None
+    lse = torch.empty((B, H, Nq), device=q.device, dtype=torch.float32) if (return_lse and writes_output) else None
     if alibi_slopes is not None:
         alibi_slopes = alibi_slopes.to(device=q.device, dtype=torch.float32).contiguous()
-    p = _params(q, k, v, out, lse, softmax_scale, causal, window, alibi_slopes, p_dropout, seed, offset, unit0,
-                num_splits, q_pos0, k_pos0)
+    if not writes_output:
+        out = None
+    p = _params(q, k, v, out if out is not None else q, lse, softmax_scale, causal, window, alibi_slopes, p_dropout,
+                seed, offset, unit0, num_splits, q_pos0, k_pos0)
+    if out is None:
+        p.o = None
+    if accum is not None:
+        o_acc, lse_acc = accum
+        if o_acc.dtype != torch.float32 or lse_acc.dtype != torch.float32 or not o_acc.is_contiguous() or \
+                not lse_acc.is_contiguous() or o_acc.shape != (B, H, Nq, d) or lse_acc.shape != (B, H, Nq):
+            raise ValueError("accum = (fp32 [B,H,Nq,d], fp32 [B,H,Nq]), contiguous")
+        p.accum_o, p.accum_lse = o_acc.data_ptr(), lse_acc.data_ptr()
+        p.accum_flags = (_lib.FA_ACCUM_FIRST if accum_first else 0) | (_lib.FA_ACCUM_FINAL if accum_final else 0)
     with torch.cuda.device(q.device):
         need = L.fa_fwd_workspace_bytes(ctypes.byref(p))
         if need:

@@ -115,7 +115,11 @@ int sm_count_of_current_device(int* sms, int* major) {
 }
 
 int validate(const fa_fwd_params* p) {
-    if (!p || !p->q || !p->k || !p->v || !p->o) return FA_ERR_INVALID_ARG;
+    if (!p || !p->q || !p->k || !p->v) return FA_ERR_INVALID_ARG;
+    // the output may be left out only by a launch that merges into a running result and is not its last
+    const bool accum_only = p->accum_o != nullptr && !(p->accum_flags & FA_ACCUM_FINAL);
+    if (!p->o && !accum_only) return FA_ERR_INVALID_ARG;
+    if (p->accum_o != nullptr && (!p->accum_lse || (reinterpret_cast<uintptr_t>(p->accum_o) & 15u))) return FA_ERR_INVALID_ARG;
     if (p->batch < 1 || p->heads < 1 || p->seqlen_q < 1 || p->seqlen_k < 1 || p->head_dim < 1) return FA_ERR_INVALID_ARG;
     if (p->heads_k < 0 || (p->heads_k > 0 && p->heads % p->heads_k != 0)) return FA_ERR_INVALID_ARG;
     if (p->dtype != FA_DTYPE_FP16 && p->dtype != FA_DTYPE_BF16) return FA_ERR_UNSUPPORTED;
@@ -177,6 +181,10 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->q_pos0 = p->q_pos0;
     a->k_pos0 = p->k_pos0;
     a->o_is_fp32 = p->o_dtype == FA_DTYPE_FP32;
+    a->accum_o = p->accum_o;
+    a->accum_lse = p->accum_lse;
+    a->accum_first = (p->accum_flags & FA_ACCUM_FIRST) ? 1 : 0;
+    a->accum_final = (p->accum_flags & FA_ACCUM_FINAL) ? 1 : 0;
     a->drop.seed_lo = static_cast<uint32_t>(p->seed);
     a->drop.seed_hi = static_cast<uint32_t>(p->seed >> 32);
     a->drop.offset = p->offset;
@@ -282,6 +290,7 @@ int fa_fwd(const fa_fwd_params* p) {
     if (rc != FA_OK) return rc;
     if (major != 10) return FA_ERR_NOT_SM100;
     const int splits = resolve_splits(p, sms);
+    if (p->accum_o != nullptr && (splits > 1 || p->head_dim % 8 != 0)) return FA_ERR_UNSUPPORTED;
     const int units = p->batch * p->heads;
     cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
     if (p->head_dim % 8 != 0) {
@@ -328,9 +337,9 @@ int fa_fwd(const fa_fwd_params* p) {
     if ((rc = make_tensor_map(&tv, bf16, p->v, p->head_dim, p->seqlen_k, units_k)) != FA_OK) return rc;
     // 16-bit output of an unsplit launch is written by TMA stores, one 32-row box per warp
     CUtensorMap to = tq;
-    a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32) ? 1 : 0;
+    a.o_tma = (splits == 1 && p->o_dtype != FA_DTYPE_FP32 && p->accum_o == nullptr) ? 1 : 0;
     if (a.o_tma && (rc = make_tensor_map(&to, bf16, p->o, p->head_dim, p->seqlen_q, units, 32)) != FA_OK) return rc;
-    if (p->seqlen_q <= 8) {
+    if (p->seqlen_q <= 8 && p->accum_o == nullptr) {
         // one to eight query rows per unit: the streaming kernel with keys on the tensor-memory lanes
         DecodeArgs d;
         std::memset(&d, 0, sizeof(d));
@@ -546,6 +555,9 @@ int fa_fwd_host(const fa_fwd_params* p) {
         q.workspace = ws_bytes ? dws : nullptr;
         q.workspace_bytes = ws_bytes;
         q.status = nullptr;
+        q.accum_o = nullptr;  // (a running result lives in device memory: not a host-buffer feature)
+        q.accum_lse = nullptr;
+        q.accum_flags = 0;
         q.stream = stream;
         result = fa_fwd(&q);
         if (result != FA_OK) break;

@@ -740,8 +740,32 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         float inv = 0.0f;
         if (l_sum > 0.0f) inv = (kDropout ? a.drop.inv_keep : 1.0f) / l_sum;
         const bool row_ok = row < a.seqlen_q;
-        const float lse_val = (l_sum > 0.0f) ? (m_ref * kLn2 + __logf(l_sum)) : -INFINITY;
+        float lse_val = (l_sum > 0.0f) ? (m_ref * kLn2 + __logf(l_sum)) : -INFINITY;
         const long long unit_ll = unit;
+        // Running result of a key sequence that arrives block by block (one launch per block: the ring
+        // of a sequence sharded across GPUs): this launch's (O, LSE) is merged into the fp32 pair the
+        // caller carries from launch to launch, with the algebra of the reference's combine kernel
+        // (src/flash_forward_splitkv.h:359-397) in its log-sum-exp form,
+        //   lse' = log(e^lse_c + e^lse),  O' = e^(lse_c - lse') O_c + e^(lse - lse') O,
+        // here in the epilogue, on the row each thread already holds, instead of in a pass of its own.
+        float w_old = 0.0f;  // weight of the carried row
+        if (a.accum_o != nullptr) {
+            const long long arow = unit_ll * a.seqlen_q + row;
+            float lse_c = -INFINITY;
+            if (!a.accum_first && row_ok) lse_c = a.accum_lse[arow];
+            const float m = fmaxf(lse_c, lse_val);
+            float lse_new = -INFINITY, w_new = 0.0f;
+            if (m != -INFINITY) {
+                const float e_old = __expf(lse_c - m), e_new = __expf(lse_val - m);
+                const float sum = e_old + e_new;
+                w_old = e_old / sum;
+                w_new = e_new / sum;
+                lse_new = m + __logf(sum);
+            }
+            inv *= w_new;
+            lse_val = lse_new;
+            if (row_ok) a.accum_lse[arow] = lse_new;
+        }
         if (a.num_splits > 1) {
             const long long prow = (unit_ll * a.num_splits + split) * a.seqlen_q + row;
             if (row_ok) a.lse_partial[prow] = lse_val;
@@ -796,6 +820,54 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             if (!row_ok) continue;
             const int col0 = c * 32;
+            if (a.accum_o != nullptr) {
+                // merged row: read-modify-write of the carried fp32 row (each thread walks its own row;
+                // the two 16-byte halves of every 32-byte sector are touched by consecutive
+                // instructions), and on the sequence's last block the 16-bit output as well
+                float* acc = a.accum_o + (unit_ll * a.seqlen_q + row) * a.head_dim;
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    if (col0 + i < a.head_dim) {
+                        float4 v4 = make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                        if (w_old != 0.0f) {
+                            const float4 c4 = *reinterpret_cast<const float4*>(acc + col0 + i);
+                            v4.x = fmaf(w_old, c4.x, v4.x);
+                            v4.y = fmaf(w_old, c4.y, v4.y);
+                            v4.z = fmaf(w_old, c4.z, v4.z);
+                            v4.w = fmaf(w_old, c4.w, v4.w);
+                        }
+                        if (!a.accum_final || a.o == nullptr) *reinterpret_cast<float4*>(acc + col0 + i) = v4;
+                        orow[i] = __float_as_uint(v4.x);
+                        orow[i + 1] = __float_as_uint(v4.y);
+                        orow[i + 2] = __float_as_uint(v4.z);
+                        orow[i + 3] = __float_as_uint(v4.w);
+                    }
+                }
+                if (a.accum_final && a.o != nullptr) {
+                    if (a.o_is_fp32) {
+                        float* dst = static_cast<float*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            if (col0 + i < a.head_dim)
+                                *reinterpret_cast<uint4*>(dst + col0 + i) = make_uint4(orow[i], orow[i + 1], orow[i + 2], orow[i + 3]);
+                    } else {
+                        uint16_t* dst = static_cast<uint16_t*>(a.o) + (unit_ll * a.seqlen_q + row) * a.head_dim;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            if (col0 + i < a.head_dim) {
+                                uint4 v4;
+                                v4.x = pack2<kBf16>(__uint_as_float(orow[i]), __uint_as_float(orow[i + 1]));
+                                v4.y = pack2<kBf16>(__uint_as_float(orow[i + 2]), __uint_as_float(orow[i + 3]));
+                                v4.z = pack2<kBf16>(__uint_as_float(orow[i + 4]), __uint_as_float(orow[i + 5]));
+                                v4.w = pack2<kBf16>(__uint_as_float(orow[i + 6]), __uint_as_float(orow[i + 7]));
+                                *reinterpret_cast<uint4*>(dst + col0 + i) = v4;
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             if (a.num_splits > 1 || a.o_is_fp32) {
                 float* dst = (a.num_splits > 1)
                                  ? a.o_partial + ((unit_ll * a.num_splits + split) * a.seqlen_q + row) * a.head_dim

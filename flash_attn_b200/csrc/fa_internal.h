@@ -42,6 +42,10 @@ struct FwdArgs {
     long long q_pos0, k_pos0;
     int o_is_fp32;
     int o_tma;              // O leaves through the TMA store map (16-bit output, unsplit launch)
+    float* accum_o;         // running fp32 result [units, Nq, d] merged in the epilogue, or null
+    float* accum_lse;       // running log-sum-exp [units, Nq]
+    int accum_first;        // nothing is carried yet: the running pair is only written
+    int accum_final;        // last block: o / lse receive the merged result (the running O is then left as it is)
     // launch order of the CTAs (filled by launch_fwd_tiled): divisors of the block index
     FastDiv div_group_ctas, div_gsize, div_last_gsize, div_splits, div_kv_group;
     DropoutParams drop;

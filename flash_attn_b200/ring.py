@@ -1,12 +1,14 @@
-"""Sequence-sharded (ring) causal attention over torch.distributed.
+"""Sequence-sharded (ring) attention: the host side of the path on torch tensors.
 
 The reference has no multi-GPU path; its softmax couples key blocks only through
 the per-row (max, sum) pair that forward_kernel_splitkv_combine merges
 (src/flash_forward_splitkv.h:359-397).  The same algebra lets a sequence be
 sharded across ranks: every rank keeps its query rows and output, the K/V shards
 travel around a ring (send to rank+1, receive from rank-1; NCCL send/recv over
-NVLink on GPUs), each visiting block contributes a partial (O, LSE) computed by
-the ordinary forward kernel with global positions, and partials are merged by LSE.
+NVLink on GPUs), and every visiting block is one launch of the ordinary forward
+kernel with global positions that merges its result into the rank's running fp32
+(O, LSE) pair in its own epilogue (fa_fwd_params.accum_o); the launch of a query
+chunk's last block also writes the 16-bit output.  No merge or cast pass runs.
 
 Layout ("zig-zag"): the sequence is cut into 2*P chunks of C rows; rank r owns
 chunks r and 2P-1-r, so with a causal mask every rank has the same amount of
@@ -41,67 +43,139 @@ def unit_slice(units, rank, world):
     return lo, lo + base + (1 if rank < extra else 0)
 
 
-def _cuda_attend(q, k, v, scale, causal, q_pos0, k_pos0):
-    return api.flash_attn_forward(q, k, v, softmax_scale=scale, causal=causal, q_pos0=q_pos0, k_pos0=k_pos0,
-                                  out_dtype=torch.float32)
+def block_visible(a, b, chunk, causal, window):
+    """Can any query of chunk `a` attend to any key of chunk `b`?  (Blocks that cannot are not launched.)"""
+    q_lo, q_hi = a * chunk, (a + 1) * chunk - 1
+    k_lo, k_hi = b * chunk, (b + 1) * chunk - 1
+    if (causal or window[1] == 0) and k_lo > q_hi:
+        return False
+    if window[1] > 0 and k_lo > q_hi + window[1]:
+        return False
+    if window[0] >= 0 and k_hi < q_lo - window[0]:
+        return False
+    return True
 
 
-def _cuda_merge(o_acc, lse_acc, o_part, lse_part):
-    api.merge_partial(o_acc, lse_acc, o_part, lse_part)
+def ring_schedule(rank, world, chunk, causal=True, window=(-1, -1)):
+    """Launches of one rank, in execution order: dicts with step (ring step), qi / ki (which of the
+    rank's query chunks, which of the visiting rank's key chunks), a / b (their global chunk
+    indices), first / final (the query chunk's first / last launch)."""
+    out = []
+    for step in range(world):
+        src = (rank - step) % world
+        for qi, a in enumerate(zigzag_chunks(rank, world)):
+            for ki, b in enumerate(zigzag_chunks(src, world)):
+                if block_visible(a, b, chunk, causal, window):
+                    out.append(dict(step=step, qi=qi, ki=ki, a=a, b=b, first=False, final=False))
+    for qi in range(2):
+        mine = [x for x in out if x["qi"] == qi]
+        if mine:
+            mine[0]["first"] = True
+            mine[-1]["final"] = True
+    return out
 
 
-def ring_attention_forward(q, k, v, group=None, softmax_scale=None, causal=True, attend_fn=None, merge_fn=None,
-                           out_dtype=None):
+def cuda_block(q, k, v, scale, causal, q_pos0, k_pos0, acc, first, final, out, window, alibi_slopes):
+    """One visiting block on the GPU: forward launch that merges into `acc` = (o_acc, lse_acc)."""
+    return api.flash_attn_forward(q, k, v, softmax_scale=scale, causal=causal, window=window, alibi_slopes=alibi_slopes,
+                                  q_pos0=q_pos0, k_pos0=k_pos0, accum=acc, accum_first=first, accum_final=final, out=out)
+
+
+class DistTransport:
+    """K/V exchange with the ring neighbours over torch.distributed (NCCL on GPUs, gloo on CPU ranks)."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.nxt, self.prv = (self.rank + 1) % self.world, (self.rank - 1) % self.world
+        if group is not None and self.world > 1:
+            self.nxt, self.prv = dist.get_global_rank(group, self.nxt), dist.get_global_rank(group, self.prv)
+
+    def exchange(self, step, send_buf, recv_buf):
+        """Posts the send of this step's K/V to rank+1 and the receive of the next step's from rank-1;
+        returns the requests to wait on before recv_buf is read."""
+        ops = [dist.P2POp(dist.isend, send_buf, self.nxt, self.group), dist.P2POp(dist.irecv, recv_buf, self.prv, self.group)]
+        return dist.batch_isend_irecv(ops)
+
+
+class LocalTransport:
+    """All ranks' K/V on one device: the 'receive' of step s+1 copies the buffer of rank r-s-1.  Runs one
+    rank's schedule exactly as the ring does, without a second GPU (tests, single-GPU runs)."""
+
+    def __init__(self, kv_of_rank, rank, world):
+        self.kv_of_rank, self.rank, self.world = kv_of_rank, rank, world
+
+    def exchange(self, step, send_buf, recv_buf):
+        recv_buf.copy_(self.kv_of_rank[(self.rank - step - 1) % self.world])
+        return []
+
+
+def pack_kv(k, v):
+    """The K/V message of a rank: one contiguous buffer [2 (k|v), 2 (chunk), B, H, C, d]."""
+    return torch.stack([torch.stack(list(k)), torch.stack(list(v))]).contiguous()
+
+
+_buffers = {}
+
+
+def _scratch(key, make):
+    """Receive buffer and running accumulators are kept between calls of the same geometry."""
+    if key not in _buffers:
+        if len(_buffers) > 8:
+            _buffers.clear()
+        _buffers[key] = make()
+    return _buffers[key]
+
+
+def ring_attention_forward(q, k, v, group=None, softmax_scale=None, causal=True, window=(-1, -1), alibi_slopes=None,
+                           p_dropout=0.0, block_fn=None, transport=None, out_dtype=None):
     """Attention over a sequence sharded in zig-zag chunks across `group`.
 
     q, k, v: lists of two [B,H,C,d] tensors (this rank's chunks, see shard_sequence).
     Returns (o, lse): lists of two tensors, [B,H,C,d] in out_dtype (default q dtype)
-    and [B,H,C] fp32.  `attend_fn(q, k, v, scale, causal, q_pos0, k_pos0) -> (o fp32,
-    lse)` and `merge_fn(o_acc, lse_acc, o_part, lse_part)` default to the CUDA
-    kernels; the CPU tests substitute the oracle.
+    and [B,H,C] fp32.  `window` and `alibi_slopes` act on global positions, as in one
+    unsharded launch.  Dropout is refused: the reference's dropout streams are keyed on
+    the tile grid of one whole-sequence launch, which a sharded launch does not have.
+    `block_fn` (default: the CUDA kernel) runs one visiting block; the CPU tests
+    substitute the oracle.  `transport` defaults to the process group.
     """
-    attend_fn = attend_fn or _cuda_attend
-    merge_fn = merge_fn or _cuda_merge
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if p_dropout:
+        raise ValueError("ring attention does not support dropout: the reference's dropout streams are keyed on "
+                         "the tile grid of a whole-sequence launch (use the head all-to-all path)")
+    block_fn = block_fn or cuda_block
+    transport = transport or DistTransport(group)
+    world, rank = transport.world, transport.rank
     B, H, C, d = q[0].shape
     scale = float(softmax_scale) if softmax_scale is not None else d ** -0.5
-    my_chunks = zigzag_chunks(rank, world)
     dev = q[0].device
-
-    o_acc = [torch.zeros((B, H, C, d), device=dev, dtype=torch.float32) for _ in range(2)]
-    lse_acc = [torch.full((B, H, C), float("-inf"), device=dev, dtype=torch.float32) for _ in range(2)]
-
-    # K/V travel as one contiguous buffer [2 (k|v), 2 (chunk), B, H, C, d], double-buffered
-    kv = [torch.stack([torch.stack(list(k)), torch.stack(list(v))]).contiguous(), None]
+    out_dtype = out_dtype or q[0].dtype
+    key = (dev, B, H, C, d, q[0].dtype, k[0].shape[1])
+    acc = _scratch(("acc",) + key, lambda: [(torch.empty((B, H, C, d), device=dev, dtype=torch.float32),
+                                             torch.empty((B, H, C), device=dev, dtype=torch.float32)) for _ in range(2)])
+    kv = [pack_kv(k, v), None]
     if world > 1:
-        kv[1] = torch.empty_like(kv[0])
-    nxt = (rank + 1) % world
-    prv = (rank - 1) % world
-    if group is not None and world > 1:
-        nxt, prv = dist.get_global_rank(group, nxt), dist.get_global_rank(group, prv)
-
+        kv[1] = _scratch(("kv",) + key, lambda: torch.empty_like(kv[0]))
+    out = [torch.empty((B, H, C, d), device=dev, dtype=out_dtype) for _ in range(2)]
+    lse = [None, None]
+    launches = ring_schedule(rank, world, C, causal, window)
     for step in range(world):
         cur = kv[step % 2]
         reqs = []
         if step + 1 < world:
             # post the exchange first: it runs on the communication stream while the kernels below compute
-            ops = [dist.P2POp(dist.isend, cur, nxt, group), dist.P2POp(dist.irecv, kv[(step + 1) % 2], prv, group)]
-            reqs = dist.batch_isend_irecv(ops)
-        src = (rank - step) % world
-        src_chunks = zigzag_chunks(src, world)
-        for qi, a in enumerate(my_chunks):
-            for ki, b in enumerate(src_chunks):
-                if causal and b > a:
-                    continue  # every key of the block lies after every query of the chunk
-                o_part, lse_part = attend_fn(q[qi], cur[0, ki], cur[1, ki], scale, causal and b == a, a * C, b * C)
-                merge_fn(o_acc[qi], lse_acc[qi], o_part, lse_part)
+            reqs = transport.exchange(step, cur, kv[(step + 1) % 2])
+        for x in (l for l in launches if l["step"] == step):
+            # blocks that lie wholly before the query chunk need no causal test
+            diag = causal and x["b"] == x["a"]
+            res = block_fn(q[x["qi"]], cur[0, x["ki"]], cur[1, x["ki"]], scale, diag, x["a"] * C, x["b"] * C,
+                           acc[x["qi"]], x["first"], x["final"], out[x["qi"]] if x["final"] else None, window, alibi_slopes)
+            if x["final"]:
+                lse[x["qi"]] = res[1]
         for r in reqs:
             r.wait()
-
-    out_dtype = out_dtype or q[0].dtype
-    if out_dtype == torch.float32:
-        return o_acc, lse_acc
-    if o_acc[0].is_cuda:
-        return [api.cast_output(o, out_dtype) for o in o_acc], lse_acc
-    return [o.to(out_dtype) for o in o_acc], lse_acc
+    for qi in range(2):
+        if lse[qi] is None:  # no key block was visible to this query chunk
+            out[qi].zero_()
+            lse[qi] = torch.full((B, H, C), float("-inf"), device=dev, dtype=torch.float32)
+    return out, lse

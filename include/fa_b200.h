@@ -84,7 +84,23 @@ typedef struct fa_fwd_params {
                                  [batch, heads_k, seqlen_k, head_dim], heads % heads_k == 0 and
                                  query head h reads K/V head h / (heads / heads_k).  0 = heads
                                  (the reference has one head count, gridDim.y, main.cu:142) */
+    /* Running result over key blocks that arrive one launch at a time (a sequence sharded across
+     * GPUs, whose K/V blocks travel round a ring).  When accum_o is set, the launch merges its
+     * (O, LSE) into the fp32 pair in its own epilogue, with the algebra of the reference's
+     * combine kernel (src/flash_forward_splitkv.h:359-397) in log-sum-exp form:
+     *   lse' = log(e^lse_acc + e^lse),  O' = e^(lse_acc-lse') O_acc + e^(lse-lse') O.
+     * Unsplit launches only (num_splits resolves to 1). */
+    float* accum_o;           /* device fp32 [B,H,Nq,head_dim], or NULL = off                     */
+    float* accum_lse;         /* device fp32 [B,H,Nq]                                             */
+    int accum_flags;          /* FA_ACCUM_FIRST: nothing is carried yet (the pair is written, not
+                                 read).  FA_ACCUM_FINAL: last block; o (o_dtype) and lse, where
+                                 non-NULL, receive the merged result, and accum_o is left as it
+                                 was (accum_lse is still updated).  Without FA_ACCUM_FINAL o may
+                                 be NULL and is not written. */
 } fa_fwd_params;
+
+#define FA_ACCUM_FIRST 1
+#define FA_ACCUM_FINAL 2
 
 /* Forward pass: O = dropout(softmax(scale*Q K^T - slope*|i-j| + masks)) V, LSE.
  * Replaces the launches of forward_kernel (src/flash_forward.h:13-306),

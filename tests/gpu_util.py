@@ -79,3 +79,34 @@ def assert_close(res, what=""):
     assert res["o_mean"] <= O_MEAN_ABS, msg
     assert res["lse_max"] <= LSE_ABS, msg
     assert res["lse_inf_match"], msg
+
+
+def check_sampled_units(q, k, v, o, lse, units, rows_of_unit, scale, causal=False, window=(-1, -1), slopes=None,
+                        q_pos0=0, k_pos0=0):
+    """Oracle comparison for tensors that live on the GPU (shapes too large to generate or check whole on the
+    host): for every sampled (batch, head) unit its K/V and the sampled query rows are copied to the host and
+    the oracle evaluates those rows.  q/o [B,H,Nq,d], k/v [B,H,Nk,d] CUDA tensors; `units` flat b*H+h indices;
+    `rows_of_unit(u)` -> row indices inside the unit.  Returns the same error dict as run_case."""
+    B, H, Nq, d = q.shape
+    o_err, lse_err, n, o_sum = 0.0, 0.0, 0, 0.0
+    inf_ok, nan = True, False
+    for u in units:
+        b, h = divmod(int(u), H)
+        rows = np.asarray(sorted(set(int(r) for r in rows_of_unit(u))), dtype=np.int64)
+        qh = q[b, h].float().cpu().numpy()[None, None]
+        kh = k[b, h % k.shape[1] if k.shape[1] == H else h // (H // k.shape[1])].float().cpu().numpy()[None, None]
+        vh = v[b, h % v.shape[1] if v.shape[1] == H else h // (H // v.shape[1])].float().cpu().numpy()[None, None]
+        want_o, want_lse = oracle_lib.forward(qh, kh, vh, scale, causal=causal, window=window,
+                                              alibi_slopes=None if slopes is None else slopes[h:h + 1],
+                                              q_pos0=q_pos0, k_pos0=k_pos0, rows=rows)
+        got_o = o[b, h].float().cpu().numpy()[rows]
+        got_lse = lse[b, h].cpu().numpy()[rows]
+        fin = np.isfinite(want_lse)
+        o_err = max(o_err, float(np.abs(got_o - want_o).max()))
+        o_sum += float(np.abs(got_o - want_o).sum())
+        n += got_o.size
+        if fin.any():
+            lse_err = max(lse_err, float(np.abs(got_lse[fin] - want_lse[fin]).max()))
+        inf_ok = inf_ok and bool(np.array_equal(np.isneginf(got_lse), np.isneginf(want_lse)))
+        nan = nan or bool(np.isnan(got_o).any() or np.isnan(got_lse).any())
+    return dict(o_max=o_err, o_mean=o_sum / max(n, 1), lse_max=lse_err, lse_inf_match=inf_ok, nan=nan)

@@ -103,3 +103,59 @@ def test_head_all_to_all_matches_single_gpu(world):
         # the same kernel on the same rows with the same mask: identical up to the summation order of
         # nothing at all (whole sequences per head), so the results are equal
         assert out[r][0] == 0.0 and out[r][1] == 0.0, out[r]
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_ring_schedule_on_one_gpu_against_the_oracle(world):
+    # every rank's loop of the ring on ONE device: all shards resident, a local transport hands over the
+    # buffers the ring would deliver, the real forward launches with global positions and the merge in
+    # their epilogue.  Checked against the CPU oracle at the chunk edges, not against the GPU kernel.
+    import numpy as np
+    import gpu_util
+    import synth
+    from flash_attn_b200 import ring
+    B, H, d, C = 1, 2, 128, 384  # chunks of three tiles
+    N = 2 * world * C
+    q, k, v = (torch.from_numpy(x).bfloat16().cuda() for x in synth.qkv(11, B, H, N, N, d, "bfloat16", 0.5))
+    kv_of_rank = [ring.pack_kv(ring.shard_sequence(k, r, world), ring.shard_sequence(v, r, world)) for r in range(world)]
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, N), device="cuda", dtype=torch.float32)
+    for r in range(world):
+        ql, kl, vl = (ring.shard_sequence(x, r, world) for x in (q, k, v))
+        o_r, lse_r = ring.ring_attention_forward(ql, kl, vl, causal=True, transport=ring.LocalTransport(kv_of_rank, r, world))
+        for i, c in enumerate(ring.zigzag_chunks(r, world)):
+            o[:, :, c * C:(c + 1) * C] = o_r[i]
+            lse[:, :, c * C:(c + 1) * C] = lse_r[i]
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(world)
+    edges = [c * C + off for c in range(2 * world) for off in (0, 1, 127, 128, C - 1)]
+    res = gpu_util.check_sampled_units(q, k, v, o, lse, [0, 1], lambda u: edges + list(rng.integers(0, N, 64)),
+                                       d ** -0.5, causal=True)
+    gpu_util.assert_close(res, f"ring schedule, {world} ranks on one GPU")
+
+
+def test_ring_with_window_and_alibi_on_one_gpu():
+    import numpy as np
+    import gpu_util
+    import synth
+    from flash_attn_b200 import ring
+    world, B, H, d, C = 4, 1, 4, 128, 256
+    N = 2 * world * C
+    q, k, v = (torch.from_numpy(x).bfloat16().cuda() for x in synth.qkv(12, B, H, N, N, d, "bfloat16", 0.5))
+    slopes = synth.alibi_slopes(H)
+    kv_of_rank = [ring.pack_kv(ring.shard_sequence(k, r, world), ring.shard_sequence(v, r, world)) for r in range(world)]
+    o = torch.empty_like(q)
+    lse = torch.empty((B, H, N), device="cuda", dtype=torch.float32)
+    for r in range(world):
+        ql, kl, vl = (ring.shard_sequence(x, r, world) for x in (q, k, v))
+        o_r, lse_r = ring.ring_attention_forward(ql, kl, vl, causal=True, window=(300, 0),
+                                                 alibi_slopes=torch.from_numpy(slopes).cuda(),
+                                                 transport=ring.LocalTransport(kv_of_rank, r, world))
+        for i, c in enumerate(ring.zigzag_chunks(r, world)):
+            o[:, :, c * C:(c + 1) * C] = o_r[i]
+            lse[:, :, c * C:(c + 1) * C] = lse_r[i]
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(2)
+    res = gpu_util.check_sampled_units(q, k, v, o, lse, range(H), lambda u: [0, 255, 256, 300, 301, N - 1] + list(rng.integers(0, N, 64)),
+                                       d ** -0.5, causal=True, window=(300, 0), slopes=slopes)
+    gpu_util.assert_close(res, "ring with window and ALiBi")
