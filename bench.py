@@ -78,6 +78,17 @@ def work_per_step(name, w):
     return flops, nbytes
 
 
+def load_ncu_traffic():
+    """DRAM bytes per launch of the dominant kernel per workload, from the ncu captures summarised under
+    profiles/ (profiles/ncu_traffic.json names the capture each figure comes from)."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -89,15 +100,32 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: NVML polled from a thread
+    (about one sample per 0.3 ms, so that a region of a few milliseconds still gets samples);
+    nvidia-smi in loop mode when NVML cannot be loaded."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, uuid):
         self.uuid, self.proc, self.lines = uuid, None, []
+        self.samples = []  # (time, sm_mhz, reasons bitmask)
+        self.nvml = None
+        self.stop_flag = False
+        self.t_mark, self.t_end = 0.0, float("inf")
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid.encode() if hasattr(self.uuid, "encode") else self.uuid)
+            self.smax = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", self.uuid, f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "20"],
@@ -107,28 +135,59 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                reasons = int(n.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception:
+                break
+            self.samples.append((time.perf_counter(), mhz, reasons))
+            time.sleep(0.0003)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append((time.perf_counter(), line.strip()))
 
     def wait_first_sample(self, limit=10.0):
         t0 = time.perf_counter()
-        while self.proc is not None and not self.lines and time.perf_counter() - t0 < limit:
+        while (self.nvml is not None or self.proc is not None) and not self.lines and not self.samples \
+                and time.perf_counter() - t0 < limit:
             time.sleep(0.01)
 
     def mark(self):
         """Samples taken before this call (warm-up) are not counted."""
         self.t_mark = time.perf_counter()
 
+    def mark_end(self):
+        """Samples taken after this call are not counted."""
+        self.t_end = time.perf_counter()
+
+    def window(self, t0, t1):
+        """Summary of the samples taken in [t0, t1] (NVML sampler only)."""
+        return self._summary([x for x in self.samples if t0 <= x[0] <= t1])
+
+    def _summary(self, rows):
+        n = self.nvml
+        names = (("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40), ("sw_power_cap", 0x4))
+        sm = sorted(r[1] for r in rows)
+        reasons = sorted({name for r in rows for name, bit in names if r[2] & bit})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": getattr(self, "smax", None),
+                "reasons": reasons, "samples": len(sm)}
+
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return self.window(self.t_mark, self.t_end)
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock sampler available"]}
         self.proc.terminate()
         self.thread.join(timeout=2)
         sm, smax, reasons = [], None, set()
-        t_mark = getattr(self, "t_mark", 0.0)
         for t, ln in self.lines:
-            if t < t_mark:
+            if t < self.t_mark or t > self.t_end:
                 continue
             parts = [x.strip() for x in ln.split(",")]
             if len(parts) < 7:
@@ -245,8 +304,10 @@ def make_inputs(torch, w, seed, device, copies):
     return sets
 
 
-def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier, sampler=None):
-    """Device-timed steps: returns seconds per step (this rank)."""
+def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier, sampler=None, sustain_seconds=0.0, unit0=None):
+    """Device-timed steps: returns (seconds per step of this rank, sustained leg or None).  The sustained
+    leg repeats the step back to back for `sustain_seconds` (long enough for the power cap to set in and
+    for the clock sampler to see it) and reports its own time per step and clocks."""
     units = w["B"] * w["H"]
     dev = sets[0][0].device
     slopes = None
@@ -254,17 +315,22 @@ def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier, sampler=
         slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / w["H"]) for h in range(w["H"])], device=dev)
     outs = [torch.empty((w["B"], w["H"], w["Nq"], w["d"]), device=dev, dtype=torch.bfloat16) for _ in sets]
     ws = torch.empty(max(16, _workspace_bytes(fa, w)), device=dev, dtype=torch.uint8)
+    unit0 = rank * units if unit0 is None else unit0
 
     def step(i):
         q, k, v = sets[i % len(sets)]
         fa.flash_attn_forward(q, k, v, causal=w["causal"], window=w["window"], alibi_slopes=slopes,
                               p_dropout=w["p"], seed=42, offset=0, num_splits=w["splits"], out=outs[i % len(sets)],
-                              unit0=rank * units, workspace=ws)
+                              unit0=unit0, workspace=ws)
 
     for i in range(warmup):
         step(i)
     barrier()
     torch.cuda.synchronize()
+    # the device idled while the ranks met at the barrier: two untimed steps bring it back to the state
+    # the warm-up left (without them the runs with a barrier measured 4 % slower than the run without)
+    for i in range(2):
+        step(i)
     if sampler is not None:
         sampler.mark()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -273,8 +339,23 @@ def time_device(torch, fa, name, w, sets, steps, warmup, rank, barrier, sampler=
         step(i)
     e1.record()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.mark_end()
     barrier()
-    return e0.elapsed_time(e1) / 1e3 / steps
+    sec = e0.elapsed_time(e1) / 1e3 / steps
+    sustained = None
+    if sustain_seconds > 0:
+        n = max(steps, int(sustain_seconds / sec) + 1)
+        t0 = time.perf_counter()
+        e0.record()
+        for i in range(n):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        sustained = {"steps": n, "seconds": e0.elapsed_time(e1) / 1e3, "ms_per_step": e0.elapsed_time(e1) / n,
+                     "clocks": sampler.window(t0, t1) if (sampler is not None and sampler.nvml is not None) else None}
+    return sec, sustained
 
 
 def _workspace_bytes(fa, w):
@@ -315,67 +396,102 @@ def time_e2e(torch, fa, w, steps, warmup, rank):
     return dt, h2d, d2h
 
 
-def run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks):
-    """Config 5: ONE problem sharded over the ranks (strong scaling): each rank holds two zig-zag
-    chunks of the sequence; K/V chunks go round the ring while the forward kernel works."""
+def measure_seq_parallel(torch, fa, w, mode, steps, warmup, rank, world, dev, barrier, max_over_ranks, sampler=None):
+    """Config 5, ONE problem sharded over the ranks (strong scaling).  mode "ring": each rank holds two
+    zig-zag chunks of the sequence, K/V chunks go round the ring (NCCL send/recv) while the forward kernel
+    works, every visiting block merged into the running result in the kernel's epilogue.  mode "ulysses":
+    head all-to-all.  Returns seconds per step (max over ranks), launches per step and rank, clocks."""
     from flash_attn_b200 import ring, ulysses
-    use_a2a = args.seq_parallel == "ulysses" and w["H"] % world == 0
     N, C = w["Nq"], w["Nq"] // (2 * world)
     g = torch.Generator(device=dev)
     g.manual_seed(5 + rank)
-    if use_a2a:
+    if mode == "ulysses":
         # contiguous slice of 2*C rows per rank; two all-to-alls trade it for whole sequences of H/P heads
         mk = lambda: (0.5 * torch.randn((w["B"], w["H"], 2 * C, w["d"]), generator=g, device=dev)).bfloat16()
+        q, k, v = mk(), mk(), mk()
         run_step = lambda: ulysses.ulysses_attention_forward(q, k, v, causal=True)
+        launches = ulysses._head_groups(w["H"], w["H"], world, 4)
     else:
         mk = lambda: [(0.5 * torch.randn((w["B"], w["H"], C, w["d"]), generator=g, device=dev)).bfloat16() for _ in range(2)]
+        q, k, v = mk(), mk(), mk()
         run_step = lambda: ring.ring_attention_forward(q, k, v, causal=True)
-    q, k, v = mk(), mk(), mk()
+        launches = len(ring.ring_schedule(rank, world, C, True))  # one forward launch per visited chunk pair
+    for _ in range(warmup):
+        run_step()
+    barrier()
+    torch.cuda.synchronize()
+    run_step()  # (the device idled at the barrier)
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run_step()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    barrier()
+    mine = e0.elapsed_time(e1) / 1e3 / steps
+    sec = max_over_ranks(mine)
+    clocks = sampler.window(t0, t1) if (sampler is not None and sampler.nvml is not None) else None
+    del q, k, v
+    torch.cuda.empty_cache()
+    return {"sec": sec, "launches": launches, "clocks": clocks, "chunk": C}
+
+
+def c5_entry(w, flops, world, m, peaks, mode):
+    value = flops / m["sec"] / 1e12
+    e = {"path": "K/V ring (NCCL send/recv, merge in the kernel epilogue)" if mode == "ring" else "head all-to-all (NCCL)",
+         "ms_per_step": m["sec"] * 1e3, "tflops": value, "tflops_per_gpu": value / world,
+         "frac_of_sustained_tensor_peak": value / world / (peaks["tensor_sustained"] or peaks["tensor"]),
+         "launches_per_step_per_rank": m["launches"], "clocks": m["clocks"]}
+    if m["clocks"] and m["clocks"].get("sm_mhz"):
+        e["tflops_per_gpu_per_mhz"] = value / world / m["clocks"]["sm_mhz"]
+    return e
+
+
+def run_c5(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks):
+    """--workload c5: the line describes the path BASELINE's config 5 names (the ring) unless
+    --seq-parallel ulysses asks for the all-to-all; the other path is measured beside it."""
+    main_mode = args.seq_parallel
+    if main_mode == "ulysses" and w["H"] % world != 0:
+        main_mode = "ring"
+    other = "ulysses" if main_mode == "ring" else "ring"
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
     if sampler:
         sampler.start()
         sampler.wait_first_sample()
-    for _ in range(args.warmup):
-        run_step()
-    barrier()
-    torch.cuda.synchronize()
+    m = measure_seq_parallel(torch, fa, w, main_mode, args.steps, args.warmup, rank, world, dev, barrier, max_over_ranks, sampler)
+    m2 = None
+    if not args.no_secondary and (other == "ring" or w["H"] % world == 0):
+        m2 = measure_seq_parallel(torch, fa, w, other, args.steps, args.warmup, rank, world, dev, barrier, max_over_ranks, sampler)
     if sampler:
-        sampler.mark()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        run_step()
-    e1.record()
-    torch.cuda.synchronize()
-    barrier()
-    sec = max_over_ranks(e0.elapsed_time(e1) / 1e3 / args.steps)
-    clocks = sampler.stop() if sampler else None
-    value = flops / sec / 1e12
-    # kernel launches per step and rank: one forward + one merge per visited (query chunk, key chunk) pair, two casts
-    pairs = sum(1 for s in range(world) for a in ring.zigzag_chunks(rank, world)
-                for b in ring.zigzag_chunks((rank - s) % world, world) if b <= a)
+        sampler.stop()
+    value = flops / m["sec"] / 1e12
+    N, C = w["Nq"], m["chunk"]
     line = {
         "metric": "fwd_attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "warmup": args.warmup, "ms_per_step": m["sec"] * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": ({"workload": w["desc"].replace("sequence ring over the ranks (zig-zag chunks, NCCL send/recv, LSE merge)",
                                                    "head all-to-all over the ranks (NCCL), whole sequences of H/P heads per rank"),
                     "rows_per_rank": 2 * C, "a2a_bytes_sent_per_rank": (4 * w["B"] * w["H"] * 2 * C * w["d"] * 2) * (world - 1) // world,
                     "l2": "each rank reads %d MB of K/V per step (> L2)" % (2 * w["B"] * w["H"] // world * N * w["d"] * 2 // 2 ** 20),
-                    "flops_per_step_total": flops} if use_a2a else
+                    "flops_per_step_total": flops} if main_mode == "ulysses" else
                    {"workload": w["desc"], "chunk_rows": C, "kv_bytes_per_ring_step_per_rank": 4 * w["B"] * w["H"] * C * w["d"] * 2,
                     "l2": "each rank streams 2 x %d MB of K/V per ring step (> L2)" % (2 * w["H"] * C * w["d"] * 2 // 2 ** 20),
                     "flops_per_step_total": flops}),
-        "clocks": clocks,
+        "clocks": m["clocks"],
         "e2e": {"value": None, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-                "note": "the ring works on device-resident shards; the host-buffer path is measured on config 2"},
-        # all-to-all: one forward launch per head group; ring: forward + merge per visited pair, two casts
-        "gpu_launches": (ulysses._head_groups(w["H"], w["H"], world, 4) if use_a2a else 2 * pairs + 2) * args.steps * world,
+                "note": "the sharded sequence lives in device memory; the host-buffer path is measured on config 2"},
+        "gpu_launches": m["launches"] * args.steps * world,
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["tensor_sustained"] or peaks["tensor"],
                      "unit": "TFLOP/s", "frac": value / world / (peaks["tensor_sustained"] or peaks["tensor"]),
                      "peak_source": peaks["source"] + " sustained (seconds-long step)", "traffic": None,
                      "kernel": "fwd_tiled_kernel"},
+        "secondary": {main_mode: c5_entry(w, flops, world, m, peaks, main_mode)},
     }
+    if m2 is not None:
+        line["secondary"][other] = c5_entry(w, flops, world, m2, peaks, other)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -391,9 +507,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
-    ap.add_argument("--seq-parallel", default="ulysses", choices=["ring", "ulysses"],
-                    help="config 5: head all-to-all (default; the faster of the two at 8 GPUs) or K/V ring with "
-                         "LSE merge (also taken when the head count is not a multiple of the GPU count)")
+    ap.add_argument("--seq-parallel", default="ring", choices=["ring", "ulysses"],
+                    help="config 5: K/V ring with the LSE merge in the kernel epilogue (default: the path the "
+                         "baseline's config 5 names) or head all-to-all; the other one is measured beside it")
     ap.add_argument("--no-secondary", action="store_true", help="skip the c3/c4 side measurements")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (for profiler runs)")
@@ -437,6 +553,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def gather_floats(x):
+        if dist is None:
+            return [x]
+        t = torch.zeros(world, device=dev, dtype=torch.float64)
+        t[rank] = x
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return [float(v) for v in t.tolist()]
+
     name = args.workload
     w = dict(WORKLOADS[name])
     if args.batch is not None:
@@ -445,7 +569,7 @@ def main():
     flops, nbytes = work_per_step(name, w)
     peaks = load_peaks()
     if name == "c5":
-        return run_ring(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks)
+        return run_c5(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, max_over_ranks)
     # two input sets (2 x 268 MB for config 2) alternate, so no step finds its inputs in the 126 MB L2
     sets = make_inputs(torch, w, 2 + rank, dev, copies=2 if not name.startswith("c4") else 1)
 
@@ -453,9 +577,11 @@ def main():
     if sampler:
         sampler.start()
         sampler.wait_first_sample()
-    sec = time_device(torch, fa, name, w, sets, args.steps, args.warmup, rank, barrier, sampler)
+    my_sec, sustained = time_device(torch, fa, name, w, sets, args.steps, args.warmup, rank, barrier, sampler,
+                                    sustain_seconds=0.0 if args.no_secondary else 0.6)
     clocks = sampler.stop() if sampler else None
-    sec = max_over_ranks(sec)
+    sec = max_over_ranks(my_sec)
+    per_rank_ms = gather_floats(my_sec * 1e3)
     del sets
     torch.cuda.empty_cache()
 
@@ -483,12 +609,14 @@ def main():
         roof["frac_of_sustained_peak"] = roof["achieved"] / peaks["tensor_sustained"]
         roof["sustained_peak"] = peaks["tensor_sustained"]
     roof["peak_source"] = peaks["source"] + (" burst" if not is_decode else " copy")
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-    # summarised under profiles/: config 2 captured at full size, config 4 captured on 128 of the
-    # 2048 units and scaled by the units processed; null where no capture of the workload exists
-    ncu_traffic = {"c2": 201.42e6 + 47.13e6, "c4": 16 * (2.1476e9 + 5.1e6)}  # no capture of c3 / c4gqa
-    roof["traffic"] = ncu_traffic.get(name) if args.batch is None else None
-    roof["traffic_source"] = "ncu capture (static figure, not measured in this run)" if roof["traffic"] else None
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the ncu captures summarised
+    # under profiles/; null where no capture of the workload exists or the batch was overridden
+    traffic = load_ncu_traffic().get(name) if args.batch is None else None
+    roof["traffic"] = traffic["bytes_per_launch"] if traffic else None
+    roof["traffic_source"] = traffic["source"] if traffic else None
+    if is_decode:
+        roof["frac_of_nominal_8tbs"] = roof["achieved"] / 8000.0
+        roof["peak_note"] = "peak is the measured read+write copy rate; a read-only stream can exceed it, see frac_of_nominal_8tbs"
     roof["kernel"] = "decode_kernel (+ combine_kernel)" if is_decode else "fwd_tiled_kernel"
     launches_per_step = 1 if w["splits"] <= 1 else 2
 
@@ -498,13 +626,23 @@ def main():
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": w["desc"], "units_per_gpu": w["B"] * w["H"], "l2": "two input sets alternate; each "
                    "step reads inputs larger than the 126 MB L2" if not is_decode else "%.1f GB streamed per step" % (nbytes / 1e9),
+                   "timed_region": "barrier + synchronize, two untimed steps (the device idled at the barrier), "
+                                   "K steps between CUDA events, synchronize + barrier",
                    "flops_per_step_per_gpu": flops, "bytes_per_step_per_gpu": nbytes},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_sec * 1e3, "api": "fa_fwd_host (pinned host buffers)"},
         "gpu_launches": launches_per_step * args.steps * world,
         "roofline": roof,
+        "per_rank_ms": per_rank_ms,
     }
+    if sustained is not None:
+        # the same step repeated back to back for >= 0.6 s: long enough to meet the power cap, with the
+        # clocks seen over exactly that stretch
+        sv = (nbytes / 1e9 if is_decode else flops / 1e12) / (sustained["ms_per_step"] / 1e3)
+        line["sustained"] = {"steps": sustained["steps"], "seconds": sustained["seconds"], "ms_per_step": sustained["ms_per_step"],
+                             "value_per_gpu": sv, "unit": unit, "clocks": sustained["clocks"],
+                             "frac_of_sustained_peak": (sv / peaks["tensor_sustained"]) if (not is_decode and peaks["tensor_sustained"]) else None}
 
     if rank == 0 and world == 1 and not args.no_secondary and name == "c2":
         side = {}
@@ -512,7 +650,7 @@ def main():
             try:
                 ow = WORKLOADS[other]
                 osets = make_inputs(torch, ow, 3, dev, copies=1)
-                osec = time_device(torch, fa, other, ow, osets, 5 if other == "c4" else 10, 3, 0, lambda: None)
+                osec, _ = time_device(torch, fa, other, ow, osets, 5 if other == "c4" else 10, 3, 0, lambda: None)
                 of, ob = work_per_step(other, ow)
                 if other.startswith("c4"):
                     side[other] = {"workload": ow["desc"], "ms": osec * 1e3, "gbs": ob / osec / 1e9,
@@ -525,6 +663,71 @@ def main():
             except Exception as exc:  # a side measurement must not lose the main line
                 side[other] = {"error": repr(exc)}
         line["secondary"] = side
+
+    if world > 1 and not args.no_secondary and name == "c2":
+        # Strong scaling beside the weak-scaling line: ONE config-2/3/4 problem whose (batch, head)
+        # units are cut into `world` slices, one per rank, with no communication ("heads sharded"),
+        # and config 5, one sequence sharded over the ranks (ring and head all-to-all).
+        strong = {}
+        for other in ("c2", "c3", "c4"):
+            try:
+                ow = dict(WORKLOADS[other])
+                total_units = ow["B"] * ow["H"]
+                lo, hi = (rank * total_units) // world, ((rank + 1) * total_units) // world
+                of, ob = work_per_step(other, ow)  # the whole problem
+                ow["B"], ow["H"] = 1, hi - lo  # this rank's slice, described as one batch of (hi - lo) heads
+                osets = make_inputs(torch, ow, 7 + rank, dev, copies=2 if other == "c2" else 1)
+                osec, _ = time_device(torch, fa, other, ow, osets, 5 if other == "c4" else 20, 3, rank, barrier, unit0=lo)
+                osec = max_over_ranks(osec)
+                e = {"workload": WORKLOADS[other]["desc"], "units_total": total_units, "units_per_rank": hi - lo,
+                     "ms": osec * 1e3, "scaling": "strong"}
+                if other == "c4":
+                    e.update(gbs=ob / osec / 1e9, gbs_per_gpu=ob / osec / 1e9 / world,
+                             frac_of_hbm_peak_per_gpu=ob / osec / 1e9 / world / peaks["hbm"])
+                else:
+                    e.update(tflops=of / osec / 1e12, tflops_per_gpu=of / osec / 1e12 / world,
+                             frac_of_tensor_peak_per_gpu=of / osec / 1e12 / world / peaks["tensor"])
+                    if other == "c3":
+                        e["note"] = "ALiBi slopes follow the slice's own head numbering (same work per head)"
+                strong[other] = e
+                del osets
+                torch.cuda.empty_cache()
+            except Exception as exc:
+                strong[other] = {"error": repr(exc)}
+        side = {"strong": strong}
+        try:
+            w5 = WORKLOADS["c5"]
+            f5, _ = work_per_step("c5", w5)
+            smp = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid)) if rank == 0 else None
+            if smp:
+                smp.start()
+                smp.wait_first_sample()
+            c5 = {"workload": w5["desc"], "scaling": "strong", "steps": 3}
+            m = measure_seq_parallel(torch, fa, w5, "ring", 3, 1, rank, world, dev, barrier, max_over_ranks, smp)
+            c5["ring"] = c5_entry(w5, f5, world, m, peaks, "ring")
+            if w5["H"] % world == 0:
+                m = measure_seq_parallel(torch, fa, w5, "ulysses", 3, 1, rank, world, dev, barrier, max_over_ranks, smp)
+                c5["ulysses"] = c5_entry(w5, f5, world, m, peaks, "ulysses")
+            if smp:
+                smp.stop()
+            side["c5"] = c5
+        except Exception as exc:
+            side["c5"] = {"error": repr(exc)}
+        line["secondary"] = side
+
+    if rank == 0 and world == 1 and not args.no_secondary and name == "c2":
+        # the C benchmark driver (no Python between the launches) on the same workload, as a cross-check
+        # of the time per launch
+        try:
+            exe = os.path.join(ROOT, "flash_attn_b200", "fa_bench")
+            if os.path.exists(exe):
+                out = subprocess.run([exe, "--config", "2", "--iters", "200", "--warmup", "10"], capture_output=True,
+                                     text=True, timeout=120)
+                r = json.loads(out.stdout.strip().splitlines()[-1])
+                line.setdefault("secondary", {})["c_driver"] = {"what": "fa_bench --config 2 (C99 over the C ABI), 200 launches",
+                                                                "ms_per_launch": r["ms_per_iter"], "tflops": r["tflops"]}
+        except Exception as exc:
+            line.setdefault("secondary", {})["c_driver"] = {"error": repr(exc)}
 
     if rank == 0 and world == 1 and not args.no_secondary and name == "c2":
         # the reference's own kernels (fp16, recompiled for sm_100a) on the same shape, for context

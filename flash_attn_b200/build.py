@@ -54,6 +54,35 @@ def build(force=False, verbose=False):
     return LIB
 
 
+TEST_LIB = os.path.join(PKG, "libfa_b200_shortwait.so")
+
+
+def build_test_variant(force=False):
+    """Builds libfa_b200_shortwait.so, the library compiled with -DFA_TEST_SHORT_WAIT: bounded waits give
+    up after about 2 ms and the producer of the tiled kernel can be told to leave one KV tile out
+    (fa_test_skip_kv_tile).  Used only by the GPU test of the give-up path."""
+    if not force and os.path.exists(TEST_LIB) and not any(
+            os.path.getmtime(os.path.join(CSRC, f)) > os.path.getmtime(TEST_LIB) for f in SOURCES + HEADERS):
+        return TEST_LIB
+    build_dir = os.path.join(PKG, "build", "shortwait")
+    os.makedirs(build_dir, exist_ok=True)
+    common = [nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-DFA_TEST_SHORT_WAIT", "-Xcompiler", "-fPIC", "-Xptxas", "-warn-spills"]
+    procs, objs = [], []
+    for src in SOURCES:
+        obj = os.path.join(build_dir, src.replace(".cu", ".o"))
+        objs.append(obj)
+        procs.append((src, subprocess.Popen(common + ["-c", os.path.join(CSRC, src), "-o", obj],
+                                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for src, pr in procs:
+        out, _ = pr.communicate()
+        if pr.returncode != 0:
+            sys.stderr.write(out)
+            raise RuntimeError(f"nvcc failed on {src} (test variant)")
+    subprocess.check_call([nvcc_path(), "-shared", "-o", TEST_LIB] + objs + ["-Xcompiler", "-fPIC"])
+    return TEST_LIB
+
+
 BENCH = os.path.join(PKG, "fa_bench")
 
 
@@ -76,3 +105,4 @@ if __name__ == "__main__":
     build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(LIB)
     print(build_driver(force="--force" in sys.argv))
+    print(build_test_variant(force="--force" in sys.argv))

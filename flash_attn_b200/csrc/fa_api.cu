@@ -410,7 +410,9 @@ struct HostStage {
     void* shim_ws = nullptr;   // workspace of fa_launch_reference_params
     size_t shim_bytes = 0;
 };
-std::mutex g_stage_mutex;
+// one lock per device ordinal: calls for different devices (one host thread per GPU) do not wait for
+// one another; calls for the same device share its staging buffers and are serialised
+std::mutex g_stage_mutex[64];
 HostStage g_stage[64];
 
 }  // namespace
@@ -418,10 +420,10 @@ HostStage g_stage[64];
 extern "C" {
 
 void fa_fwd_host_release(void) {
-    std::lock_guard<std::mutex> lock(g_stage_mutex);
     int prev = 0;
     cudaGetDevice(&prev);
     for (int d = 0; d < 64; ++d) {
+        std::lock_guard<std::mutex> lock(g_stage_mutex[d]);
         HostStage& st = g_stage[d];
         if (!st.buf && !st.streams[0] && !st.shim_ws) continue;
         cudaSetDevice(d);
@@ -461,7 +463,7 @@ int fa_launch_reference_params(const fa_ref_kernel_params* param, int heads, int
     if (need) {
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FA_ERR_CUDA;
-        std::lock_guard<std::mutex> lock(g_stage_mutex);
+        std::lock_guard<std::mutex> lock(g_stage_mutex[dev]);
         HostStage& st = g_stage[dev];
         if (st.shim_bytes < need) {
             // the old buffer may still be in use by an earlier launch on another stream
@@ -486,7 +488,7 @@ int fa_fwd_host(const fa_fwd_params* p) {
     if (rc != FA_OK) return rc;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FA_ERR_CUDA;
-    std::lock_guard<std::mutex> lock(g_stage_mutex);
+    std::lock_guard<std::mutex> lock(g_stage_mutex[dev]);
     HostStage& st = g_stage[dev];
     for (auto& s : st.streams)
         if (!s && cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) return FA_ERR_CUDA;
@@ -537,7 +539,11 @@ int fa_fwd_host(const fa_fwd_params* p) {
         char* dlse = dout + align(o_unit * per);
         char* dslopes = dlse + align(lse_unit * per);
         char* dws = dslopes + align(sizeof(float) * per);
-        bool ok = cudaMemcpyAsync(dq, static_cast<const char*>(p->q) + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+        int* dstatus = reinterpret_cast<int*>(dws + align(ws_bytes));
+        // the word the kernels set when one of their bounded waits gives up: cleared once per slot, read
+        // back after the streams have drained (a slice that timed out leaves it set for the rest of the call)
+        bool ok = s >= 2 || cudaMemsetAsync(dstatus, 0, sizeof(int), stream) == cudaSuccess;
+        ok = ok && cudaMemcpyAsync(dq, static_cast<const char*>(p->q) + u0 * q_unit, n * q_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
         ok = ok && cudaMemcpyAsync(dk, static_cast<const char*>(p->k) + (u0 / group) * kv_unit, (n / group) * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
         ok = ok && cudaMemcpyAsync(dv, static_cast<const char*>(p->v) + (u0 / group) * kv_unit, (n / group) * kv_unit, cudaMemcpyHostToDevice, stream) == cudaSuccess;
         if (ok && p->alibi_slopes)
@@ -554,7 +560,7 @@ int fa_fwd_host(const fa_fwd_params* p) {
         q.num_splits = splits;
         q.workspace = ws_bytes ? dws : nullptr;
         q.workspace_bytes = ws_bytes;
-        q.status = nullptr;
+        q.status = dstatus;
         q.accum_o = nullptr;  // (a running result lives in device memory: not a host-buffer feature)
         q.accum_lse = nullptr;
         q.accum_flags = 0;
@@ -568,6 +574,16 @@ int fa_fwd_host(const fa_fwd_params* p) {
     }
     for (auto& s : st.streams)
         if (cudaStreamSynchronize(s) != cudaSuccess && result == FA_OK) result = FA_ERR_CUDA;
+    if (result == FA_OK) {
+        const long long n_slices = (units + per - 1) / per;
+        for (int b = 0; b < 2 && b < n_slices; ++b) {
+            int hs = 0;
+            const char* slot_base = static_cast<const char*>(st.buf) + b * slot;
+            const char* word = slot_base + (slot - align(sizeof(int)));
+            if (cudaMemcpy(&hs, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return FA_ERR_CUDA;
+            if (hs != 0) result = FA_ERR_DEVICE_TIMEOUT;
+        }
+    }
     return result;
 }
 

@@ -56,6 +56,19 @@ extern "C" int fa_trace_read(long long* host_out) {
 #define FA_TR(ev) do { } while (0)
 #endif
 
+// Test build only (-DFA_TEST_SHORT_WAIT): the producer can be told to leave out the loads of one KV
+// tile, so that a consumer's bounded wait runs out and the give-up path (status word, drain, TMEM
+// release, clean exit) can be checked on a GPU without faulting or hanging anything.
+#ifdef FA_TEST_SHORT_WAIT
+__device__ int fa_test_skip_tile = -1;
+extern "C" int fa_test_skip_kv_tile(int t) {
+    return static_cast<int>(cudaMemcpyToSymbol(fa_test_skip_tile, &t, sizeof(int)));
+}
+#define FA_TEST_SKIPS(t) (fa_test_skip_tile == (t))
+#else
+#define FA_TEST_SKIPS(t) false
+#endif
+
 namespace fa {
 
 namespace {
@@ -366,6 +379,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             prefilled = min(C::kStages, n_union);
             for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
+                if (FA_TEST_SKIPS(t)) continue;
                 const int row = (hi - 1 - t) * kTile;  // KV tiles are walked from the last to the first
                 mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
 #pragma unroll
@@ -412,6 +426,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // ======================= TMA producer ===================================
             if (lane == 0) {
                 for (int t = prefilled; t < n_union; ++t) {
+                    if (FA_TEST_SKIPS(t)) continue;
                     const int st = t % C::kStages;
                     const uint32_t ph = (t / C::kStages) & 1;
                     const int row = (hi - 1 - t) * kTile;

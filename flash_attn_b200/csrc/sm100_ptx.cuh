@@ -11,7 +11,11 @@ namespace fa {
 
 // Every spin in the kernels is bounded: after kWaitCycles SM clocks a wait gives
 // up, records a code in the status word and the CTA drains to its exit.
+#ifdef FA_TEST_SHORT_WAIT
+constexpr long long kWaitCycles = 1LL << 22;  // ~2 ms: the test build, whose give-up path is exercised on purpose
+#else
 constexpr long long kWaitCycles = 4000000000LL;  // ~2 s at 1.9 GHz
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -15,6 +15,10 @@
  * Ownership: the caller owns every buffer including the workspace; the library
  * allocates nothing in fa_fwd and keeps no state between calls (there is no RNG
  * state array: dropout is a function of (seed, offset) only).
+ * Threads: every entry point may be called from several host threads at once, on
+ * the same or on different devices (the current device is the thread's, as in the
+ * CUDA runtime).  fa_fwd_host and fa_launch_reference_params serialise the calls
+ * of one device on its cached buffers; calls for different devices run concurrently.
  */
 #ifndef FA_B200_H
 #define FA_B200_H
@@ -39,7 +43,7 @@ extern "C" {
 #define FA_ERR_UNSUPPORTED (-2)    /* head_dim > 128, dtype combination                            */
 #define FA_ERR_WORKSPACE (-3)      /* workspace missing or smaller than fa_fwd_workspace_bytes()   */
 #define FA_ERR_CUDA (-4)           /* a CUDA runtime/driver call failed                            */
-#define FA_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait gave up (read from *status)       */
+#define FA_ERR_DEVICE_TIMEOUT (-5) /* a bounded device-side wait gave up (fa_fwd_host; see status)    */
 #define FA_ERR_NOT_SM100 (-6)      /* the current device is not compute capability 10.x            */
 #define FA_ERR_TOO_LARGE (-7)      /* size beyond a fixed limit of the entry point                 */
 
@@ -78,7 +82,12 @@ typedef struct fa_fwd_params {
                                  behaviour; used to run one block of a sharded sequence)      */
     void* workspace;          /* device; split partials (param.O_tmp, param.L, param.M) */
     size_t workspace_bytes;
-    int* status;              /* device int or NULL: set non-zero if a device wait timed out */
+    int* status;              /* device int or NULL.  Every wait inside the kernels is bounded (about 2 s of SM
+                                 clocks); a wait that gives up stores a code here -- 100 + n from the tiled
+                                 forward kernel, 200 + n from the decode kernel, n naming the wait -- and the
+                                 CTA drains and exits, leaving O and LSE undefined.  fa_fwd is asynchronous:
+                                 the caller clears the word before the launch and reads it after synchronising
+                                 the stream.  fa_fwd_host does both itself and returns FA_ERR_DEVICE_TIMEOUT. */
     void* stream;             /* cudaStream_t; NULL = default stream (the reference's)       */
     int heads_k;              /* K/V heads for grouped-query attention: K and V are
                                  [batch, heads_k, seqlen_k, head_dim], heads % heads_k == 0 and
