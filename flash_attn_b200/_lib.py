@@ -40,6 +40,7 @@ class FwdParams(ctypes.Structure):
         ("stream", ctypes.c_void_p),
         ("heads_k", ctypes.c_int),
         ("accum_o", ctypes.c_void_p), ("accum_lse", ctypes.c_void_p), ("accum_flags", ctypes.c_int),
+        ("launch_index", ctypes.c_uint64),
     ]
 
 

@@ -46,7 +46,7 @@ def _params(q, k, v, o, lse, softmax_scale, causal, window, alibi_slopes, p_drop
 def flash_attn_forward(q, k, v, softmax_scale=None, causal=False, window=(-1, -1), alibi_slopes=None,
                        p_dropout=0.0, seed=0, offset=0, num_splits=1, out=None, out_dtype=None, return_lse=True,
                        q_pos0=0, k_pos0=0, unit0=0, workspace=None, status=None, accum=None, accum_first=False,
-                       accum_final=False):
+                       accum_final=False, launch_index=0):
     """O, LSE = attention(Q, K, V) on the current CUDA device and stream.
 
     q [B,H,Nq,d], k/v [B,Hk,Nk,d] (Hk divides H; query head h reads K/V head
@@ -77,6 +77,7 @@ def flash_attn_forward(q, k, v, softmax_scale=None, causal=False, window=(-1, -1
                 seed, offset, unit0, num_splits, q_pos0, k_pos0)
     if out is None:
         p.o = None
+    p.launch_index = int(launch_index)  # dropout mask of the k-th launch of a loop of the reference's kernels
     if accum is not None:
         o_acc, lse_acc = accum
         if o_acc.dtype != torch.float32 or lse_acc.dtype != torch.float32 or not o_acc.is_contiguous() or \
@@ -120,7 +121,7 @@ def flash_attn_forward_host(q, k, v, softmax_scale=None, causal=False, window=(-
 
 
 def dropout_mask(B, H, Nq, Nk, p_dropout, seed, offset=0, num_splits=1, window_left=-1, q_pos0=0, k_pos0=0,
-                 unit0=0, device="cuda"):
+                 unit0=0, device="cuda", causal=False, window_right=-1, launch_index=0):
     """uint8 [B,H,Nq,Nk] keep-mask (1 = kept) that flash_attn_forward applies."""
     L = _lib.load()
     keep = torch.empty((B, H, Nq, Nk), device=device, dtype=torch.uint8)
@@ -130,10 +131,12 @@ def dropout_mask(B, H, Nq, Nk, p_dropout, seed, offset=0, num_splits=1, window_l
     p.dtype = p.o_dtype = _lib.FA_DTYPE_FP16
     p.batch, p.heads, p.seqlen_q, p.seqlen_k, p.head_dim = B, H, Nq, Nk, 64
     p.softmax_scale = 1.0
-    p.window_left, p.window_right = int(window_left), -1
+    p.window_left, p.window_right = int(window_left), int(window_right)
+    p.is_causal = int(bool(causal))
     p.p_dropout, p.seed, p.offset, p.unit0 = float(p_dropout), int(seed), int(offset), int(unit0)
     p.num_splits = int(num_splits)
     p.q_pos0, p.k_pos0 = int(q_pos0), int(k_pos0)
+    p.launch_index = int(launch_index)
     with torch.cuda.device(keep.device):
         p.stream = torch.cuda.current_stream(keep.device).cuda_stream
         _lib.check(L.fa_dropout_mask(ctypes.byref(p), keep.data_ptr()), "fa_dropout_mask")

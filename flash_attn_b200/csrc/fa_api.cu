@@ -188,6 +188,7 @@ void fill_args(const fa_fwd_params* p, int splits, FwdArgs* a) {
     a->drop.seed_lo = static_cast<uint32_t>(p->seed);
     a->drop.seed_hi = static_cast<uint32_t>(p->seed >> 32);
     a->drop.offset = p->offset;
+    a->drop.launch_index = p->launch_index;
     a->drop.unit0 = p->unit0;
     a->drop.threshold = p->p_dropout > 0.0f ? keep_threshold(p->p_dropout) : 0ull;
     a->drop.inv_keep = p->p_dropout > 0.0f ? 1.0f / (1.0f - p->p_dropout) : 1.0f;

@@ -116,9 +116,21 @@ __global__ void dropout_mask_kernel(const FwdArgs a, uint8_t* keep, long long to
         split = cb / a.tiles_per_split;
         lo = a.tiles_per_split * split;
     }
+    int hi = a.num_splits > 1 ? min(lo + a.tiles_per_split, a.tc) : a.tc;
+    const long long q0 = a.q_pos0 + static_cast<long long>(rb) * kTile;
     if (a.window_left >= 0) {
-        const long long w = (a.q_pos0 + static_cast<long long>(rb) * kTile - a.window_left - a.k_pos0) / kTile;
+        const long long w = (q0 - a.window_left - a.k_pos0) / kTile;
         lo = max(lo, static_cast<int>(max(0LL, min(w, static_cast<long long>(a.tc)))));
+    }
+    // upper end of the CTA's tile range (src/flash_forward.h:42-48): it decides how far a later launch
+    // of a loop has advanced the stream
+    if (a.window_right >= 0) {
+        const long long last = q0 + kTile - 1 + a.window_right - a.k_pos0;
+        hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
+    }
+    if (a.is_causal) {
+        const long long last = q0 + kTile - 1 - a.k_pos0;
+        hi = min(hi, last < 0 ? 0 : static_cast<int>(min(last / kTile + 1, static_cast<long long>(a.tc))));
     }
     const unsigned long long subseq =
         (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
@@ -129,7 +141,7 @@ __global__ void dropout_mask_kernel(const FwdArgs a, uint8_t* keep, long long to
     const int w = 2 * ((cc % 16) / 8) + (cc % 2);
     uint8_t k = 1;
     if (cb >= lo) {
-        const uint32_t bits = philox_keep4(a.drop, subseq, 64ull * (cb - lo) + 8ull * i + 4ull * half);
+        const uint32_t bits = philox_keep4(a.drop, subseq, continuation(a.drop, hi - lo) + 64ull * (cb - lo) + 8ull * i + 4ull * half);
         k = (bits >> w) & 1u;
     }
     keep[idx] = k;

@@ -408,7 +408,8 @@ decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant_
                             const unsigned long long subseq =
                                 (a.drop.unit0 + unit + n / sq) * static_cast<unsigned long long>(a.num_splits) +
                                 static_cast<unsigned long long>(split);
-                            const unsigned long long first = 64ull * static_cast<unsigned long long>(c * kChunkTiles + t) +
+                            const unsigned long long first = continuation(a.drop, n_tiles) +
+                                                             64ull * static_cast<unsigned long long>(c * kChunkTiles + t) +
                                                              8ull * (r >> 4);
                             const uint32_t bits = philox_keep4(a.drop, subseq, first);
                             kept = (bits >> (2 * ((r >> 3) & 1) + (r & 1))) & 1u;

@@ -565,10 +565,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
         // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
         // tile ahead, while the warp would otherwise wait for S.
+        const unsigned long long drop_cont = kDropout ? continuation(a.drop, n_tiles) : 0ull;
         auto tile_keep_bits = [&](int j) -> uint32_t {
             if constexpr (!kDropout) return 0xffffffffu;
             uint32_t mine = 0;
-            if (lane < 16) mine = philox_keep4(a.drop, subseq, 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
+            if (lane < 16) mine = philox_keep4(a.drop, subseq, drop_cont + 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
             const int half = (lane >> 3) & 1;
             uint32_t bits = 0;
 #pragma unroll

@@ -10,6 +10,8 @@
 // row%16 in 8*(j/4) + {0..7}.  Draw n of a stream is word n%4 of the Philox block
 // with counter (n/4, subsequence) and key = seed; it is dropped iff
 // x*2^-32 + 2^-33 < p in fp32, i.e. iff x < keep_threshold(p).
+// Later launches of a timing loop: the kernels save the advanced state, so the CTA that
+// visits T KV tiles starts launch k at draw 64*k*T of its stream (continuation()).
 #pragma once
 #include <cstdint>
 
@@ -18,6 +20,9 @@ namespace fa {
 struct DropoutParams {
     uint32_t seed_lo, seed_hi;
     unsigned long long offset;      // draws skipped at the start of every stream
+    unsigned long long launch_index;  // the reference writes every stream's state back (src/flash_forward.h:302-305):
+                                      // launch k of a loop continues each CTA's stream 64 * k * (KV tiles that CTA
+                                      // visits) draws further on; 0 = the first launch
     unsigned long long unit0;       // global (b*H+h) index of this launch's first unit
     unsigned long long threshold;   // raw draws below this are dropped (may be 2^32)
     float inv_keep;                 // 1/(1-p)
@@ -39,6 +44,11 @@ __host__ __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1,
         k1 += 0xBB67AE85u;
     }
     out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+// Draws a stream is ahead by at launch dp.launch_index when its CTA visits `tiles_visited` KV tiles per launch.
+__host__ __device__ __forceinline__ unsigned long long continuation(const DropoutParams& dp, int tiles_visited) {
+    return dp.launch_index * 64ull * static_cast<unsigned long long>(tiles_visited > 0 ? tiles_visited : 0);
 }
 
 // Keep bits of draws first .. first+3 of stream `subseq` (first % 4 == 0 before

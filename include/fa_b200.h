@@ -106,6 +106,12 @@ typedef struct fa_fwd_params {
                                  non-NULL, receive the merged result, and accum_o is left as it
                                  was (accum_lse is still updated).  Without FA_ACCUM_FINAL o may
                                  be NULL and is not written. */
+    uint64_t launch_index;    /* dropout in a loop of launches: the reference's kernels write every CTA's
+                                 generator state back (src/flash_forward.h:302-305), so launch k of its
+                                 timing loop (src/main.cu:195-206) continues each stream 64*k*T draws
+                                 further on, T = KV tiles that CTA visits (fewer under a causal or local
+                                 mask, so one `offset` cannot express it).  launch_index = k reproduces
+                                 the mask of that launch; 0 = the first launch. */
 } fa_fwd_params;
 
 #define FA_ACCUM_FIRST 1

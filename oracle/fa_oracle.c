@@ -105,6 +105,26 @@ int fa_oracle_dropout_keep(const fa_oracle_dropout_geom* g, int b, int h, int64_
     /* tiles left of the window are never visited by the CTA: nothing is drawn
      * for them (and every element there is masked anyway) */
     if (cb < nbmin) return 1;
+    /* Later launches of a loop: the kernels store the advanced state back
+     * (flash_forward.h:302-305), so launch k starts every stream 64 draws per
+     * visited tile per earlier launch further on.  Visited tiles = the CTA's loop
+     * range [n_block_min, n_block_max), flash_forward.h:39-48 and
+     * flash_forward_splitkv.h:40-52. */
+    uint64_t ahead = 0;
+    if (g->launch_index > 0) {
+        int64_t nbmax = splits == 1 ? Tc : imin64(per * s + per, Tc);
+        const int64_t q_end = g->q_pos0 + (rb + 1) * TILE - g->k_pos0; /* (bx+1)*Br with positions */
+        if (g->window_right >= 0) {
+            const int64_t last = q_end - 1 + g->window_right;
+            nbmax = imin64(nbmax, last < 0 ? 0 : last / TILE + 1);
+        }
+        if (g->causal) {
+            const int64_t last = q_end - 1;
+            nbmax = imin64(nbmax, last < 0 ? 0 : last / TILE + 1);
+        }
+        const int64_t lo = imin64(nbmin, Tc);
+        if (nbmax > lo) ahead = g->launch_index * 64ull * (uint64_t)(nbmax - lo);
+    }
     /* one stream per CTA: flash_forward.h:52 with grid (Tr*splits, H, B) */
     const uint64_t subseq = ((uint64_t)b * g->heads + h) * (uint64_t)(Tr * splits) + (uint64_t)(rb * splits + s);
     /* 64 draws per KV tile in c_frag[i][j] order (flash_forward.h:223-227); the
@@ -115,7 +135,7 @@ int fa_oracle_dropout_keep(const fa_oracle_dropout_geom* g, int b, int h, int64_
     const int rr = (int)(row % TILE), cc = (int)(col % TILE);
     const int i = cc / 16;
     const int j = 4 * ((rr % 16) / 8) + 2 * ((cc % 16) / 8) + (cc % 2);
-    const uint64_t n = 64ull * (uint64_t)(cb - nbmin) + 8ull * i + j;
+    const uint64_t n = ahead + 64ull * (uint64_t)(cb - nbmin) + 8ull * i + j;
     const uint32_t x = fa_oracle_curand_draw(g->seed, subseq, g->offset, n);
     return !(fa_oracle_uniform(x) < g->p);
 }
@@ -186,6 +206,7 @@ static void attend_row(const fa_oracle_params* p, int b, int h, int64_t i,
         g.num_splits = p->dropout_splits < 1 ? 1 : p->dropout_splits;
         g.causal = p->causal; g.window_left = p->window_left;
         g.q_pos0 = p->q_pos0; g.k_pos0 = p->k_pos0;
+        g.window_right = p->window_right; g.launch_index = p->launch_index;
         const float keep_scale = 1.0f / (1.0f - p->p_dropout);
         for (int64_t j = 0; j < Nk; ++j) {
             if (scores[j] == 0.0f) continue;

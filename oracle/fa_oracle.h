@@ -45,9 +45,13 @@ typedef struct {
     int seqlen_q;         /* rows; Tr = ceil(seqlen_q/128)                  */
     int seqlen_k;         /* columns; Tc = ceil(seqlen_k/128)               */
     int num_splits;       /* 1 = non-split launch                           */
-    int causal;           /* unused by the map itself, kept for callers     */
+    int causal;           /* bounds the CTA's tile range (launch_index)     */
     int window_left;      /* < 0: no local mask (n_block_min = 0)           */
     int64_t q_pos0, k_pos0; /* global positions of row 0 / column 0          */
+    int window_right;     /* < 0: off; bounds the tile range (launch_index) */
+    uint64_t launch_index; /* k-th launch of a loop over the same generator
+                             states (flash_forward.h:302-305): every stream
+                             has advanced 64 * k * (tiles its CTA visits)   */
 } fa_oracle_dropout_geom;
 
 /* 1 if P[b,h,row,col] is kept, 0 if dropped, for the reference's draw order. */
@@ -75,6 +79,7 @@ typedef struct {
     float* o;             /* [B,H,Nq,d] or [n_rows,d]                       */
     float* lse;           /* [B,H,Nq]   or [n_rows]   (may be NULL)         */
     int num_threads;      /* <= 0: all available                            */
+    uint64_t launch_index; /* dropout mask of the k-th launch of a loop      */
 } fa_oracle_params;
 
 /* Naive fp32 attention, restating reference src/main.cu:279-388 step by step. */

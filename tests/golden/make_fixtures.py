@@ -104,7 +104,8 @@ def heuristic(libref):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("FA_REFERENCE_DIR"), required="FA_REFERENCE_DIR" not in os.environ,
+                    help="path of the reference checkout (or the environment variable FA_REFERENCE_DIR)")
     args = ap.parse_args()
     subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle"), f"REF={args.reference}", "all"])
     curand_vectors()

@@ -18,7 +18,8 @@ class DropoutGeom(ctypes.Structure):
     _fields_ = [("seed", ctypes.c_uint64), ("offset", ctypes.c_uint64), ("p", ctypes.c_float),
                 ("heads", ctypes.c_int), ("seqlen_q", ctypes.c_int), ("seqlen_k", ctypes.c_int),
                 ("num_splits", ctypes.c_int), ("causal", ctypes.c_int), ("window_left", ctypes.c_int),
-                ("q_pos0", ctypes.c_int64), ("k_pos0", ctypes.c_int64)]
+                ("q_pos0", ctypes.c_int64), ("k_pos0", ctypes.c_int64),
+                ("window_right", ctypes.c_int), ("launch_index", ctypes.c_uint64)]
 
 
 class Params(ctypes.Structure):
@@ -31,7 +32,7 @@ class Params(ctypes.Structure):
                 ("seed", ctypes.c_uint64), ("offset", ctypes.c_uint64), ("dropout_splits", ctypes.c_int),
                 ("q_pos0", ctypes.c_int64), ("k_pos0", ctypes.c_int64),
                 ("rows", c_i64), ("n_rows", ctypes.c_int64),
-                ("o", c_f), ("lse", c_f), ("num_threads", ctypes.c_int)]
+                ("o", c_f), ("lse", c_f), ("num_threads", ctypes.c_int), ("launch_index", ctypes.c_uint64)]
 
 
 def lib():
@@ -59,7 +60,7 @@ def lib():
 
 
 def forward(q, k, v, scale, causal=False, window=(-1, -1), alibi_slopes=None, p_dropout=0.0, seed=0,
-            offset=0, dropout_splits=1, q_pos0=0, k_pos0=0, rows=None, num_threads=0):
+            offset=0, dropout_splits=1, q_pos0=0, k_pos0=0, rows=None, num_threads=0, launch_index=0):
     """q [B,H,Nq,d], k/v [B,H,Nk,d] fp32 numpy.  Returns (o, lse) for all rows, or
     for the flat row indices in `rows` ((b*H+h)*Nq + i)."""
     q = np.ascontiguousarray(q, dtype=np.float32)
@@ -91,15 +92,18 @@ def forward(q, k, v, scale, causal=False, window=(-1, -1), alibi_slopes=None, p_
         lse = np.empty((B, H, Nq), dtype=np.float32)
     p.o, p.lse = o.ctypes.data_as(c_f), lse.ctypes.data_as(c_f)
     p.num_threads = int(num_threads)
+    p.launch_index = int(launch_index)
     rc = lib().fa_oracle_forward(ctypes.byref(p))
     if rc != 0:
         raise RuntimeError(f"fa_oracle_forward failed: {rc}")
     return o, lse
 
 
-def dropout_mask(B, H, Nq, Nk, p, seed, offset=0, num_splits=1, window_left=-1, q_pos0=0, k_pos0=0):
+def dropout_mask(B, H, Nq, Nk, p, seed, offset=0, num_splits=1, window_left=-1, q_pos0=0, k_pos0=0, causal=False,
+                 window_right=-1, launch_index=0):
     g = DropoutGeom(seed=seed, offset=offset, p=p, heads=H, seqlen_q=Nq, seqlen_k=Nk, num_splits=num_splits,
-                    causal=0, window_left=window_left, q_pos0=q_pos0, k_pos0=k_pos0)
+                    causal=int(causal), window_left=window_left, q_pos0=q_pos0, k_pos0=k_pos0,
+                    window_right=window_right, launch_index=launch_index)
     out = np.empty((B, H, Nq, Nk), dtype=np.uint8)
     for b in range(B):
         for h in range(H):

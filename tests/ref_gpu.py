@@ -21,15 +21,17 @@ def lib():
         L = ctypes.CDLL(PATH)
         L.ref_gpu_forward.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 4 + [ctypes.c_float, ctypes.c_int,
                                       ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_float,
-                                      ctypes.c_ulonglong, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_float)]
+                                      ctypes.c_ulonglong, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_float),
+                                      ctypes.c_int]
         L.ref_gpu_forward.restype = ctypes.c_int
         _L = L
     return _L
 
 
 def forward(q, k, v, scale, causal=False, window=(-1, -1), slopes=None, p_dropout=0.0, seed=0, split_num=1,
-            iters=0):
-    """q/k/v fp16 CUDA [B,H,N,d].  Returns (o fp32, splits used, mean us per launch or None)."""
+            iters=0, prior_launches=0):
+    """q/k/v fp16 CUDA [B,H,N,d].  Returns (o fp32, splits used, mean us per launch or None).
+    prior_launches: launches made on the same generator states before the one that is returned."""
     B, H, N, d = q.shape
     o = torch.zeros((B, H, N, d), device=q.device, dtype=torch.float32)
     t = ctypes.c_float(0.0)
@@ -37,7 +39,7 @@ def forward(q, k, v, scale, causal=False, window=(-1, -1), slopes=None, p_dropou
     rc = lib().ref_gpu_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), B, H, N, d, float(scale),
                                int(causal), int(window[0]), int(window[1]),
                                slopes.data_ptr() if slopes is not None else None, float(p_dropout), int(seed),
-                               int(split_num), int(iters), ctypes.byref(t))
+                               int(split_num), int(iters), ctypes.byref(t), int(prior_launches))
     if rc < 0:
         raise RuntimeError(f"ref_gpu_forward failed: {rc}")
     return o, rc, (t.value if iters > 0 else None)

@@ -17,14 +17,18 @@ import synth
 pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not ref_gpu.available(), reason="reference kernels not built")]
 
 
-def _reference_mask(B, H, N, p, seed, split_num=1):
+def _reference_mask(B, H, N, p, seed, split_num=1, causal=False, prior_launches=0):
+    """Keep mask the reference kernel applies in launch number `prior_launches` on one set of generator states
+    (entries a causal mask hides read as 0)."""
     d, tiles = 128, (N + 127) // 128
     q = torch.zeros(B, H, N, d, dtype=torch.float16, device="cuda")
     v = torch.zeros(B, H, N, d, dtype=torch.float32, device="cuda")
     idx = torch.arange(N, device="cuda")
     v[:, :, idx, idx % 128] = (2.0 ** (idx // 128)).float()
-    o, used, _ = ref_gpu.forward(q, q, v.half(), 1.0, p_dropout=p, seed=seed, split_num=split_num)
-    code = torch.round(o * (N * (1.0 - np.float32(p).item()))).to(torch.int64)
+    o, used, _ = ref_gpu.forward(q, q, v.half(), 1.0, causal=causal, p_dropout=p, seed=seed, split_num=split_num,
+                                 prior_launches=prior_launches)
+    visible = (idx + 1).float() if causal else torch.full((N,), float(N), device="cuda")  # keys each row attends to
+    code = torch.round(o * (visible * (1.0 - np.float32(p).item()))[None, None, :, None]).to(torch.int64)
     keep = torch.zeros(B, H, N, tiles * 128, dtype=torch.uint8, device="cuda")
     for t in range(tiles):
         keep[..., t * 128:(t + 1) * 128] = ((code >> t) & 1).to(torch.uint8)
@@ -101,3 +105,30 @@ def test_launch_with_the_reference_parameter_block():
     o_ref, _, _ = ref_gpu.forward(q, k, v, d ** -0.5, causal=True, p_dropout=0.1, seed=48)
     err = (o - o_ref).abs()
     assert err.max().item() <= gpu_util.O_MAX_ABS and err.mean().item() <= gpu_util.O_MEAN_ABS
+
+
+@pytest.mark.parametrize("case", [dict(N=384, causal=False, k=1), dict(N=512, causal=True, k=1), dict(N=512, causal=True, k=3),
+                                  dict(N=512, causal=False, k=2, split_num=2), dict(N=512, causal=True, k=2, split_num=2)])
+def test_later_launches_of_the_reference_loop_continue_the_streams(case):
+    # the reference writes the generator states back (src/flash_forward.h:302-305): launch k of its loop
+    # starts every CTA's stream 64 draws per visited KV tile per earlier launch further on -- fewer tiles for
+    # the upper query blocks of a causal launch, so a single offset cannot express it.  launch_index does.
+    import flash_attn_b200 as fa
+    B, H, N, p, seed, k = 1, 2, case["N"], 0.1, 48, case["k"]
+    splits, causal = case.get("split_num", 1), case["causal"]
+    got_ref, _ = _reference_mask(B, H, N, p, seed, splits, causal=causal, prior_launches=k)
+    first, _ = _reference_mask(B, H, N, p, seed, splits, causal=causal)
+    visible = np.tril(np.ones((N, N), dtype=bool)) if causal else np.ones((N, N), dtype=bool)
+    assert not np.array_equal(got_ref, first)  # the loop really moves on
+    want = oracle_lib.dropout_mask(B, H, N, N, np.float32(p).item(), seed, 0, splits, causal=causal, launch_index=k)
+    assert np.array_equal(got_ref[..., visible], want[..., visible])
+    ours = fa.dropout_mask(B, H, N, N, p, seed, 0, splits, causal=causal, launch_index=k).cpu().numpy()
+    assert np.array_equal(ours[..., visible], got_ref[..., visible])
+    # and the forward kernel applies that mask: same launch of the reference kernels, same numbers
+    q, kk, v = (gpu_util.to_dev(x, "float16") for x in synth.qkv(43, B, H, N, N, 128, "float16"))
+    o_ref, _, _ = ref_gpu.forward(q, kk, v, 128 ** -0.5, causal=causal, p_dropout=p, seed=seed, split_num=splits,
+                                  prior_launches=k)
+    o, _ = fa.flash_attn_forward(q, kk, v, causal=causal, p_dropout=p, seed=seed, num_splits=splits,
+                                 out_dtype=torch.float32, launch_index=k)
+    err = (o - o_ref).abs()
+    assert err.max().item() <= gpu_util.O_MAX_ABS and err.mean().item() <= gpu_util.O_MEAN_ABS, (err.max(), err.mean())
