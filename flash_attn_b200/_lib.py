@@ -15,7 +15,8 @@ FA_ACCUM_FIRST, FA_ACCUM_FINAL = 1, 2
 #: every symbol include/fa_b200.h declares
 EXPORTS = ["fa_fwd", "fa_fwd_workspace_bytes", "fa_fwd_resolve_splits", "fa_num_splits_heuristic",
            "fa_dropout_mask", "fa_merge_partial", "fa_cast_output", "fa_fwd_host", "fa_fwd_host_release",
-           "fa_fwd_static_scratch", "fa_static_scratch_bytes", "fa_launch_reference_params", "fa_strerror", "fa_version"]
+           "fa_fwd_static_scratch", "fa_static_scratch_bytes", "fa_launch_reference_params", "fa_strerror", "fa_version",
+           "fa_ring_fwd", "fa_ring_message_bytes", "fa_ring_unique_id", "fa_ring_comm_create", "fa_ring_comm_destroy"]
 
 
 class FwdParams(ctypes.Structure):
@@ -41,6 +42,26 @@ class FwdParams(ctypes.Structure):
         ("heads_k", ctypes.c_int),
         ("accum_o", ctypes.c_void_p), ("accum_lse", ctypes.c_void_p), ("accum_flags", ctypes.c_int),
         ("launch_index", ctypes.c_uint64),
+    ]
+
+
+class RingParams(ctypes.Structure):
+    """struct fa_ring_params"""
+    _fields_ = [
+        ("q", ctypes.c_void_p * 2), ("k", ctypes.c_void_p * 2), ("v", ctypes.c_void_p * 2), ("o", ctypes.c_void_p * 2),
+        ("lse", ctypes.c_void_p * 2),
+        ("dtype", ctypes.c_int), ("batch", ctypes.c_int), ("heads", ctypes.c_int), ("heads_k", ctypes.c_int),
+        ("chunk_rows", ctypes.c_int), ("head_dim", ctypes.c_int),
+        ("softmax_scale", ctypes.c_float),
+        ("is_causal", ctypes.c_int), ("window_left", ctypes.c_int), ("window_right", ctypes.c_int),
+        ("alibi_slopes", ctypes.c_void_p),
+        ("p_dropout", ctypes.c_float),
+        ("rank", ctypes.c_int), ("world", ctypes.c_int),
+        ("comm", ctypes.c_void_p),
+        ("message", ctypes.c_void_p * 2),
+        ("accum_o", ctypes.c_void_p * 2), ("accum_lse", ctypes.c_void_p * 2),
+        ("compute_stream", ctypes.c_void_p), ("comm_stream", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
     ]
 
 
@@ -101,6 +122,18 @@ def load():
     L.fa_merge_partial.restype = ctypes.c_int
     L.fa_cast_output.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_void_p]
     L.fa_cast_output.restype = ctypes.c_int
+    rp = ctypes.POINTER(RingParams)
+    L.fa_ring_fwd.argtypes = [rp]
+    L.fa_ring_fwd.restype = ctypes.c_int
+    L.fa_ring_message_bytes.argtypes = [rp]
+    L.fa_ring_message_bytes.restype = ctypes.c_size_t
+    L.fa_ring_unique_id.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+    L.fa_ring_unique_id.restype = ctypes.c_int
+    L.fa_ring_comm_create.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                      ctypes.c_size_t]
+    L.fa_ring_comm_create.restype = ctypes.c_int
+    L.fa_ring_comm_destroy.argtypes = [ctypes.c_void_p]
+    L.fa_ring_comm_destroy.restype = ctypes.c_int
     L.fa_strerror.argtypes = [ctypes.c_int]
     L.fa_strerror.restype = ctypes.c_char_p
     L.fa_version.argtypes = []

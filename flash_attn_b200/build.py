@@ -12,7 +12,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libfa_b200.so")
-SOURCES = ["fa_api.cu", "fa_fwd_tiled.cu", "fa_decode.cu", "fa_aux.cu", "fa_static_scratch.cu"]
+SOURCES = ["fa_api.cu", "fa_fwd_tiled.cu", "fa_decode.cu", "fa_aux.cu", "fa_static_scratch.cu", "fa_ring.cu"]
 HEADERS = ["fa_internal.h", "sm100_ptx.cuh", "philox.cuh", os.path.join("..", "..", "include", "fa_b200.h")]
 
 
@@ -50,7 +50,7 @@ def build(force=False, verbose=False):
             sys.stderr.write(out)
         if pr.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}")
-    subprocess.check_call([nvcc_path(), "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC"])
+    subprocess.check_call([nvcc_path(), "-shared", "-o", LIB] + objs + ["-Xcompiler", "-fPIC", "-ldl"])
     return LIB
 
 
@@ -79,7 +79,7 @@ def build_test_variant(force=False):
         if pr.returncode != 0:
             sys.stderr.write(out)
             raise RuntimeError(f"nvcc failed on {src} (test variant)")
-    subprocess.check_call([nvcc_path(), "-shared", "-o", TEST_LIB] + objs + ["-Xcompiler", "-fPIC"])
+    subprocess.check_call([nvcc_path(), "-shared", "-o", TEST_LIB] + objs + ["-Xcompiler", "-fPIC", "-ldl"])
     return TEST_LIB
 
 
@@ -96,7 +96,7 @@ def build_driver(force=False):
     cc = "/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc"
     subprocess.check_call([cc, "-std=c99", "-O2", "-Wall", "-I", os.path.join(PKG, "..", "include"),
                            "-I", os.path.join(cuda, "include"), src, "-o", BENCH,
-                           "-L", PKG, "-lfa_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm",
+                           "-L", PKG, "-lfa_b200", "-L", os.path.join(cuda, "lib64"), "-lcudart", "-lm", "-lpthread",
                            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(cuda, "lib64")])
     return BENCH
 

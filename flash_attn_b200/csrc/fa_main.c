@@ -8,13 +8,17 @@
  * can be dumped to a file; the tests compare that dump with the CPU oracle (the
  * reference's in-program verfiy(), src/main.cu:254-276, is replaced by that check).
  *
- *   fa_bench --config 1|2|3|4 [--gpus N] [--iters I] [--warmup W] [--dump FILE] [--units U]
+ *   fa_bench --config 1|2|3|4|5 [--gpus N] [--iters I] [--warmup W] [--dump FILE] [--units U]
  *
- * With --gpus N the (batch, head) units are cut into N contiguous slices, one per
- * device, with no communication; every device gets its own stream and the job time
- * is the slowest device's.  Plain C99: only the CUDA runtime API and fa_b200.h.
+ * With --gpus N the (batch, head) units of configs 1-4 are cut into N contiguous slices,
+ * one per device, with no communication; every device gets its own stream and the job
+ * time is the slowest device's.  Config 5 is ONE sequence sharded over the N devices:
+ * one host thread per device runs fa_ring_fwd (K/V ring over NCCL send/recv, merge in the
+ * kernel epilogue).  Plain C99: only the CUDA runtime API, pthreads and fa_b200.h.
  */
+#define _POSIX_C_SOURCE 200112L /* pthread barriers under -std=c99 */
 #include <math.h>
+#include <pthread.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -94,6 +98,136 @@ static void fill(uint16_t* dst, size_t n, uint64_t seed, uint64_t stream, float 
     }
 }
 
+
+/* ---- config 5: bf16 [1,32,131072,128] causal, N(0, 0.5), the sequence sharded over the devices ---- */
+typedef struct {
+    int rank, world, iters, warmup, heads, chunk, d, rc;
+    void* comm;
+    const uint16_t* host_chunk[3][2];  /* one head of q, k, v for each of the rank's two chunks */
+    pthread_barrier_t* barrier;
+    float ms;
+} ring_thread_t;
+
+static void* ring_thread(void* arg) {
+    ring_thread_t* t = (ring_thread_t*)arg;
+    t->rc = 1;
+    if (cudaSetDevice(t->rank) != cudaSuccess) return NULL;
+    const size_t head_elems = (size_t)t->chunk * t->d, chunk_elems = head_elems * t->heads;
+    cudaStream_t compute, comm;
+    cudaEvent_t e0, e1;
+    if (cudaStreamCreate(&compute) != cudaSuccess || cudaStreamCreate(&comm) != cudaSuccess ||
+        cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return NULL;
+    fa_ring_params p;
+    memset(&p, 0, sizeof(p));
+    void* dev_in[3][2];
+    for (int x = 0; x < 3; ++x)
+        for (int i = 0; i < 2; ++i) {
+            if (cudaMalloc(&dev_in[x][i], chunk_elems * 2) != cudaSuccess) return NULL;
+            /* one generated head, repeated over the heads on the device */
+            if (cudaMemcpy(dev_in[x][i], t->host_chunk[x][i], head_elems * 2, cudaMemcpyHostToDevice) != cudaSuccess) return NULL;
+            for (int h = 1; h < t->heads; ++h)
+                if (cudaMemcpy((char*)dev_in[x][i] + (size_t)h * head_elems * 2, dev_in[x][i], head_elems * 2,
+                               cudaMemcpyDeviceToDevice) != cudaSuccess) return NULL;
+        }
+    for (int i = 0; i < 2; ++i) {
+        p.q[i] = dev_in[0][i]; p.k[i] = dev_in[1][i]; p.v[i] = dev_in[2][i];
+        if (cudaMalloc(&p.o[i], chunk_elems * 2) != cudaSuccess) return NULL;
+        if (cudaMalloc((void**)&p.lse[i], (size_t)t->heads * t->chunk * 4) != cudaSuccess) return NULL;
+        if (cudaMalloc((void**)&p.accum_o[i], chunk_elems * 4) != cudaSuccess) return NULL;
+        if (cudaMalloc((void**)&p.accum_lse[i], (size_t)t->heads * t->chunk * 4) != cudaSuccess) return NULL;
+    }
+    p.dtype = FA_DTYPE_BF16;
+    p.batch = 1; p.heads = t->heads; p.heads_k = t->heads; p.chunk_rows = t->chunk; p.head_dim = t->d;
+    p.softmax_scale = 1.0f / sqrtf((float)t->d);
+    p.is_causal = 1; p.window_left = p.window_right = -1;
+    p.rank = t->rank; p.world = t->world; p.comm = t->comm;
+    p.compute_stream = compute; p.comm_stream = comm;
+    const size_t msg = fa_ring_message_bytes(&p);
+    if (cudaMalloc(&p.message[0], msg) != cudaSuccess || cudaMalloc(&p.message[1], msg) != cudaSuccess) return NULL;
+    for (int it = 0; it < t->warmup; ++it)
+        if (fa_ring_fwd(&p) != FA_OK) return NULL;
+    if (cudaDeviceSynchronize() != cudaSuccess) return NULL;
+    pthread_barrier_wait(t->barrier);
+    cudaEventRecord(e0, compute);
+    for (int it = 0; it < t->iters; ++it)
+        if (fa_ring_fwd(&p) != FA_OK) return NULL;
+    cudaEventRecord(e1, compute);
+    if (cudaStreamSynchronize(compute) != cudaSuccess || cudaStreamSynchronize(comm) != cudaSuccess) return NULL;
+    cudaEventElapsedTime(&t->ms, e0, e1);
+    pthread_barrier_wait(t->barrier);
+    for (int i = 0; i < 2; ++i) {
+        cudaFree((void*)p.q[i]); cudaFree((void*)p.k[i]); cudaFree((void*)p.v[i]); cudaFree(p.o[i]); cudaFree(p.lse[i]);
+        cudaFree(p.accum_o[i]); cudaFree(p.accum_lse[i]); cudaFree(p.message[i]);
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1); cudaStreamDestroy(compute); cudaStreamDestroy(comm);
+    t->rc = 0;
+    return NULL;
+}
+
+typedef struct { int g, world, rc; unsigned char* id; void** comm; } fa_bench_ci_t;
+static void* fa_bench_comm_thread(void* arg) {
+    fa_bench_ci_t* c = (fa_bench_ci_t*)arg;
+    c->rc = 1;
+    if (cudaSetDevice(c->g) != cudaSuccess) return NULL;
+    if (fa_ring_comm_create(c->comm, c->world, c->g, c->id, 128) != FA_OK) return NULL;
+    c->rc = 0;
+    return NULL;
+}
+
+static int run_config5(int gpus, int iters, int warmup, int seq) {
+    const int heads = 32, d = 128;
+    if (seq % (2 * gpus * 128) != 0) { fprintf(stderr, "fa_bench: the sequence must split into 2 x gpus chunks of whole tiles\n"); return 2; }
+    const int chunk = seq / (2 * gpus);
+    unsigned char id[128];
+    void** comms = (void**)calloc((size_t)gpus, sizeof(void*));
+    ring_thread_t* th = (ring_thread_t*)calloc((size_t)gpus, sizeof(ring_thread_t));
+    pthread_t* tid = (pthread_t*)calloc((size_t)gpus, sizeof(pthread_t));
+    pthread_barrier_t barrier;
+    pthread_barrier_init(&barrier, NULL, (unsigned)gpus);
+    if (gpus > 1) CHECK_FA(fa_ring_unique_id(id, sizeof(id)));
+    /* one generated head per chunk of the sequence (2 x gpus chunks), shared by q, k, v streams 0, 1, 2 */
+    const size_t head_elems = (size_t)chunk * d;
+    uint16_t* host = (uint16_t*)malloc(head_elems * 2 * 3 * 2 * (size_t)gpus);
+    if (!host) { fprintf(stderr, "fa_bench: out of host memory\n"); return 1; }
+    for (int g = 0; g < gpus; ++g) {
+        const int chunks[2] = {g, 2 * gpus - 1 - g};
+        for (int x = 0; x < 3; ++x)
+            for (int i = 0; i < 2; ++i) {
+                uint16_t* dst = host + (((size_t)g * 3 + x) * 2 + i) * head_elems;
+                for (size_t e = 0; e < head_elems; ++e)
+                    dst[e] = to_bf16(synth_normal(5, (uint64_t)x, (uint64_t)chunks[i] * head_elems + e, 0.5f));
+                th[g].host_chunk[x][i] = dst;
+            }
+    }
+    for (int g = 0; g < gpus; ++g) {
+        th[g].rank = g; th[g].world = gpus; th[g].iters = iters; th[g].warmup = warmup;
+        th[g].heads = heads; th[g].chunk = chunk; th[g].d = d; th[g].barrier = &barrier;
+    }
+    if (gpus > 1) {
+        /* ncclCommInitRank blocks until all ranks have called it: one thread per rank */
+        pthread_t* it = (pthread_t*)calloc((size_t)gpus, sizeof(pthread_t));
+        fa_bench_ci_t* ci = (fa_bench_ci_t*)calloc((size_t)gpus, sizeof(fa_bench_ci_t));
+        for (int g = 0; g < gpus; ++g) { ci[g].g = g; ci[g].world = gpus; ci[g].id = id; ci[g].comm = &comms[g]; pthread_create(&it[g], NULL, fa_bench_comm_thread, &ci[g]); }
+        for (int g = 0; g < gpus; ++g) pthread_join(it[g], NULL);
+        for (int g = 0; g < gpus; ++g) if (ci[g].rc != 0) { fprintf(stderr, "fa_bench: communicator of rank %d failed\n", g); return 1; }
+        free(it); free(ci);
+    }
+    for (int g = 0; g < gpus; ++g) { th[g].comm = comms[g]; pthread_create(&tid[g], NULL, ring_thread, &th[g]); }
+    float ms_max = 0.0f;
+    int bad = 0;
+    for (int g = 0; g < gpus; ++g) { pthread_join(tid[g], NULL); if (th[g].rc) bad = 1; if (th[g].ms > ms_max) ms_max = th[g].ms; }
+    for (int g = 0; g < gpus; ++g) if (comms[g]) { cudaSetDevice(g); fa_ring_comm_destroy(comms[g]); }
+    if (bad) { fprintf(stderr, "fa_bench: a ring rank failed\n"); return 1; }
+    const double ms_iter = ms_max / iters;
+    const double flops = 4.0 * heads * 0.5 * (double)seq * (double)seq * d;  /* causal convention 4*H*N^2*d/2 */
+    printf("{\"driver\": \"fa_bench\", \"config\": \"config 5: bf16 [1,32,%d,128] causal, sequence ring over %d GPU(s)\", "
+           "\"n_gpus\": %d, \"iters\": %d, \"ms_per_iter\": %.4f, \"tflops\": %.2f, \"chunk_rows\": %d}\n",
+           seq, gpus, gpus, iters, ms_iter, flops / (ms_iter * 1e-3) / 1e12, chunk);
+    free(host); free(th); free(tid); free(comms);
+    pthread_barrier_destroy(&barrier);
+    return 0;
+}
+
 typedef struct {
     int dev, units, unit0;
     void *q, *k, *v, *o, *ws, *slopes;
@@ -105,7 +239,7 @@ typedef struct {
 } shard_t;
 
 int main(int argc, char** argv) {
-    int cfg_id = 1, gpus = 1, iters = 20, warmup = 3, units_override = 0;
+    int cfg_id = 1, gpus = 1, iters = 20, warmup = 3, units_override = 0, seq = 131072;
     const char* dump = NULL;
     for (int i = 1; i < argc; ++i) {
         if (!strcmp(argv[i], "--config") && i + 1 < argc) cfg_id = atoi(argv[++i]);
@@ -114,9 +248,16 @@ int main(int argc, char** argv) {
         else if (!strcmp(argv[i], "--warmup") && i + 1 < argc) warmup = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--units") && i + 1 < argc) units_override = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--dump") && i + 1 < argc) dump = argv[++i];
-        else { fprintf(stderr, "usage: fa_bench --config 1..4 [--gpus N] [--iters I] [--warmup W] [--units U] [--dump FILE]\n"); return 2; }
+        else if (!strcmp(argv[i], "--seq") && i + 1 < argc) seq = atoi(argv[++i]);  /* config 5: sequence length (tests) */
+        else { fprintf(stderr, "usage: fa_bench --config 1..5 [--gpus N] [--iters I] [--warmup W] [--units U] [--dump FILE] [--seq N]\n"); return 2; }
     }
-    if (cfg_id < 1 || cfg_id > 4 || gpus < 1 || iters < 1) { fprintf(stderr, "fa_bench: bad arguments\n"); return 2; }
+    if (cfg_id < 1 || cfg_id > 5 || gpus < 1 || iters < 1) { fprintf(stderr, "fa_bench: bad arguments\n"); return 2; }
+    if (cfg_id == 5) {
+        int ndev5 = 0;
+        CHECK_CUDA(cudaGetDeviceCount(&ndev5));
+        if (gpus > ndev5) { fprintf(stderr, "fa_bench: %d GPUs asked, %d present\n", gpus, ndev5); return 2; }
+        return run_config5(gpus, iters, warmup, seq);
+    }
     config_t c = kConfigs[cfg_id - 1];
     int units = c.B * c.H;
     if (units_override > 0 && units_override < units) units = units_override;  /* a prefix of the units (tests) */

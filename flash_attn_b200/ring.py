@@ -179,3 +179,86 @@ def ring_attention_forward(q, k, v, group=None, softmax_scale=None, causal=True,
             out[qi].zero_()
             lse[qi] = torch.full((B, H, C), float("-inf"), device=dev, dtype=torch.float32)
     return out, lse
+
+
+# ------------------------------------------------------------------ the same ring through the C ABI
+
+def create_ring_comm(group=None):
+    """NCCL communicator for fa_ring_fwd, one per rank: rank 0 asks the library for an id and the
+    process group hands it round.  Returns an opaque handle (destroy_ring_comm frees it)."""
+    import ctypes
+    from . import _lib
+    L = _lib.load()
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    if world == 1:
+        return None
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ident = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        buf = (ctypes.c_ubyte * 128)()
+        _lib.check(L.fa_ring_unique_id(buf, 128), "fa_ring_unique_id")
+        ident = torch.tensor(list(buf), dtype=torch.uint8)
+    ident = ident.to(dev) if dist.get_backend(group) == "nccl" else ident
+    dist.broadcast(ident, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    raw = bytes(ident.cpu().tolist())
+    comm = ctypes.c_void_p()
+    with torch.cuda.device(dev):
+        _lib.check(L.fa_ring_comm_create(ctypes.byref(comm), world, rank, raw, 128), "fa_ring_comm_create")
+    return comm
+
+
+def destroy_ring_comm(comm):
+    from . import _lib
+    if comm is not None:
+        _lib.load().fa_ring_comm_destroy(comm)
+
+
+_comm_streams = {}
+
+
+def ring_attention_forward_c(q, k, v, comm, rank, world, softmax_scale=None, causal=True, window=(-1, -1),
+                             alibi_slopes=None):
+    """ring_attention_forward with the whole schedule -- exchange, launches, stream ordering -- inside
+    the library (fa_ring_fwd): torch only owns the memory.  q, k, v as in ring_attention_forward; `comm`
+    from create_ring_comm (None when world == 1)."""
+    import ctypes
+    from . import _lib
+    L = _lib.load()
+    B, H, C, d = q[0].shape
+    Hk = k[0].shape[1]
+    dev = q[0].device
+    p = _lib.RingParams()
+    out = [torch.empty_like(q[0]) for _ in range(2)]
+    lse = [torch.empty((B, H, C), device=dev, dtype=torch.float32) for _ in range(2)]
+    key = (dev, B, H, Hk, C, d, q[0].dtype)
+    acc = _scratch(("c_acc",) + key, lambda: [(torch.empty((B, H, C, d), device=dev, dtype=torch.float32),
+                                               torch.empty((B, H, C), device=dev, dtype=torch.float32)) for _ in range(2)])
+    for i in range(2):
+        for t in (q[i], k[i], v[i]):
+            if not t.is_contiguous():
+                raise ValueError("chunks must be contiguous")
+        p.q[i], p.k[i], p.v[i] = q[i].data_ptr(), k[i].data_ptr(), v[i].data_ptr()
+        p.o[i], p.lse[i] = out[i].data_ptr(), lse[i].data_ptr()
+        p.accum_o[i], p.accum_lse[i] = acc[i][0].data_ptr(), acc[i][1].data_ptr()
+    p.dtype = api._DT[q[0].dtype]
+    p.batch, p.heads, p.heads_k, p.chunk_rows, p.head_dim = B, H, Hk, C, d
+    p.softmax_scale = float(softmax_scale) if softmax_scale is not None else d ** -0.5
+    p.is_causal, p.window_left, p.window_right = int(bool(causal)), int(window[0]), int(window[1])
+    slopes = None
+    if alibi_slopes is not None:
+        slopes = alibi_slopes.to(device=dev, dtype=torch.float32).contiguous()
+        p.alibi_slopes = slopes.data_ptr()
+    p.rank, p.world = rank, world
+    p.comm = comm
+    nbytes = L.fa_ring_message_bytes(ctypes.byref(p))
+    msgs = _scratch(("c_msg",) + key, lambda: [torch.empty(nbytes, device=dev, dtype=torch.uint8) for _ in range(2)])
+    p.message[0], p.message[1] = msgs[0].data_ptr(), msgs[1].data_ptr()
+    if dev not in _comm_streams:
+        _comm_streams[dev] = torch.cuda.Stream(device=dev)
+    with torch.cuda.device(dev):
+        cur = torch.cuda.current_stream(dev)
+        p.compute_stream = cur.cuda_stream
+        p.comm_stream = _comm_streams[dev].cuda_stream
+        _lib.check(L.fa_ring_fwd(ctypes.byref(p)), "fa_ring_fwd")
+    return out, lse

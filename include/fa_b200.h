@@ -222,6 +222,53 @@ int fa_launch_reference_params(const fa_ref_kernel_params* param, int heads, int
 int fa_fwd_static_scratch(const fa_fwd_params* p);
 size_t fa_static_scratch_bytes(void);
 
+/*
+ * Ring attention: the forward pass of ONE rank of a sequence sharded across the GPUs of an NCCL
+ * communicator.  No counterpart in the reference (one GPU); the merge of the visiting key blocks is
+ * the algebra of its combine kernel (src/flash_forward_splitkv.h:359-397), done in the forward
+ * kernel's epilogue (accum_o above).  The sequence of 2*world*chunk_rows positions is cut into
+ * 2*world chunks; rank r holds chunks r and 2*world-1-r ("zig-zag": equal causal work per rank) of Q,
+ * K and V and produces the same chunks of O and LSE.  K/V travel round the ring as one message per
+ * step (ncclSend to rank+1 / ncclRecv from rank-1 on comm_stream) while compute_stream runs one
+ * forward launch per visible (query chunk, key chunk) pair.  Asynchronous: returns once everything is
+ * enqueued; O/LSE are complete when compute_stream has drained.  The caller owns every buffer.
+ * Dropout is not supported (FA_ERR_UNSUPPORTED): the reference's dropout streams are keyed on the tile
+ * grid of one whole-sequence launch.  NCCL is looked up at run time (libnccl.so.2); without it only
+ * world = 1 works.
+ */
+typedef struct fa_ring_params {
+    const void* q[2];         /* device, dtype, [batch, heads,   chunk_rows, head_dim]: chunks r, 2*world-1-r */
+    const void* k[2];         /* device, dtype, [batch, heads_k, chunk_rows, head_dim]                        */
+    const void* v[2];
+    void* o[2];               /* device, dtype, like q                                                        */
+    float* lse[2];            /* device fp32 [batch, heads, chunk_rows], or NULL                               */
+    int dtype;                /* FA_DTYPE_FP16 | FA_DTYPE_BF16 */
+    int batch, heads, heads_k;/* heads_k = 0 means heads */
+    int chunk_rows, head_dim;
+    float softmax_scale;
+    int is_causal, window_left, window_right;  /* on global positions, as in one unsharded launch */
+    const float* alibi_slopes;/* device fp32 [heads] or NULL */
+    float p_dropout;          /* must be 0 */
+    int rank, world;
+    void* comm;               /* ncclComm_t of the ring (may be NULL when world == 1) */
+    void* message[2];         /* device, fa_ring_message_bytes() each: the K/V message at hand and the one
+                                 being received ([1] may be NULL when world == 1) */
+    float* accum_o[2];        /* device fp32, like q: running results (scratch; contents on return undefined) */
+    float* accum_lse[2];      /* device fp32 [batch, heads, chunk_rows] */
+    void* compute_stream;     /* cudaStream_t of the forward launches */
+    void* comm_stream;        /* cudaStream_t of the exchange; must differ from compute_stream when world > 1 */
+    int* status;              /* as in fa_fwd_params */
+} fa_ring_params;
+int fa_ring_fwd(const fa_ring_params* p);
+/* Bytes of one K/V message buffer (K and V of the rank's two chunks). */
+size_t fa_ring_message_bytes(const fa_ring_params* p);
+/* Communicator helpers for callers that have no NCCL code of their own: rank 0 asks for an id
+ * (128 bytes) and hands it to the other ranks by any means; every rank, with its device current,
+ * then creates its communicator.  (Wrappers of ncclGetUniqueId / ncclCommInitRank / ncclCommDestroy.) */
+int fa_ring_unique_id(void* id_out, size_t bytes);
+int fa_ring_comm_create(void** comm_out, int world, int rank, const void* id, size_t bytes);
+int fa_ring_comm_destroy(void* comm);
+
 /* Message for a return code. */
 const char* fa_strerror(int code);
 int fa_version(void);

@@ -159,3 +159,68 @@ def test_ring_with_window_and_alibi_on_one_gpu():
     res = gpu_util.check_sampled_units(q, k, v, o, lse, range(H), lambda u: [0, 255, 256, 300, 301, N - 1] + list(rng.integers(0, N, 64)),
                                        d ** -0.5, causal=True, window=(300, 0), slopes=slopes)
     gpu_util.assert_close(res, "ring with window and ALiBi")
+
+
+def test_c_abi_ring_with_one_rank_matches_the_oracle():
+    # fa_ring_fwd with world = 1: both chunks of the sequence on this GPU, no exchange
+    import numpy as np
+    import gpu_util
+    import synth
+    from flash_attn_b200 import ring
+    B, H, d, C = 1, 2, 128, 384
+    N = 2 * C
+    q, k, v = (torch.from_numpy(x).bfloat16().cuda() for x in synth.qkv(13, B, H, N, N, d, "bfloat16", 0.5))
+    ql, kl, vl = (ring.shard_sequence(x, 0, 1) for x in (q, k, v))
+    o_l, lse_l = ring.ring_attention_forward_c(ql, kl, vl, None, 0, 1, causal=True)
+    torch.cuda.synchronize()
+    o = torch.cat(o_l, dim=2)
+    lse = torch.cat(lse_l, dim=2)
+    rng = np.random.default_rng(1)
+    res = gpu_util.check_sampled_units(q, k, v, o, lse, [0, 1], lambda u: [0, 127, 128, C - 1, C, N - 1] + list(rng.integers(0, N, 64)),
+                                       d ** -0.5, causal=True)
+    gpu_util.assert_close(res, "fa_ring_fwd, one rank")
+
+
+def _c_ring_worker(rank, world, port, out):
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from datetime import timedelta
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, timeout=timedelta(seconds=60),
+                            device_id=torch.device("cuda", rank))
+    comm = None
+    try:
+        from flash_attn_b200 import ring
+        import synth
+        B, H, N, d = 1, 4, 1024 * world, 128
+        q, k, v = (torch.from_numpy(x).bfloat16().cuda() for x in synth.qkv(9, B, H, N, N, d, "bfloat16", 0.5))
+        ql, kl, vl = (ring.shard_sequence(x, rank, world) for x in (q, k, v))
+        comm = ring.create_ring_comm()
+        o_c, lse_c = ring.ring_attention_forward_c(ql, kl, vl, comm, rank, world, causal=True)
+        o_c2, lse_c2 = ring.ring_attention_forward_c(ql, kl, vl, comm, rank, world, causal=True)  # buffers reused
+        o_py, lse_py = ring.ring_attention_forward(ql, kl, vl, causal=True)
+        torch.cuda.synchronize()
+        # the same launches in the same order on the same data: equal bit for bit
+        same = all(torch.equal(a, b) for a, b in zip(o_c + lse_c + o_c2 + lse_c2, o_py + lse_py + o_py + lse_py))
+        out[rank] = bool(same)
+    except Exception as exc:
+        out[rank] = repr(exc)
+    finally:
+        if comm is not None:
+            from flash_attn_b200 import ring
+            ring.destroy_ring_comm(comm)
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_c_abi_ring_equals_the_python_ring(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_c_ring_worker, args=(world, 29300 + os.getpid() % 200, out), nprocs=world, join=True)
+    for r in range(world):
+        assert out[r] is True, out[r]
