@@ -78,6 +78,32 @@ def work_per_step(name, w):
     return flops, nbytes
 
 
+def pin_to_gpu_node(torch, dev):
+    """Keeps this rank's threads, and with them the pages of the pinned host buffers it allocates, on the
+    CPUs next to its GPU (the PCI device's local_cpulist): the host-buffer path then crosses no socket
+    link.  Returns what was done, for the JSON line."""
+    try:
+        pr = torch.cuda.get_device_properties(dev)
+        bdf = "%04x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bdf}/local_cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            if "-" in part:
+                a, b = part.split("-")
+                cpus.update(range(int(a), int(b) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        if use:
+            os.sched_setaffinity(0, use)
+            return {"pci": bdf, "local_cpulist": text, "cpus_used": len(use)}
+        return {"pci": bdf, "local_cpulist": text, "cpus_used": 0, "note": "no local CPU is allowed to this process"}
+    except (OSError, ValueError, AttributeError) as exc:
+        return {"error": repr(exc)}
+
+
 def load_ncu_traffic():
     """DRAM bytes per launch of the dominant kernel per workload, from the ncu captures summarised under
     profiles/ (profiles/ncu_traffic.json names the capture each figure comes from)."""
@@ -536,6 +562,7 @@ def main():
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    affinity = pin_to_gpu_node(torch, dev)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -631,7 +658,9 @@ def main():
                    "flops_per_step_per_gpu": flops, "bytes_per_step_per_gpu": nbytes},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_sec * 1e3, "api": "fa_fwd_host (pinned host buffers)"},
+                "ms_per_step": e2e_sec * 1e3, "api": "fa_fwd_host (pinned host buffers)",
+                "host_gbs_per_gpu": (h2d + d2h) / e2e_sec / 1e9, "host_gbs_all_gpus": world * (h2d + d2h) / e2e_sec / 1e9,
+                "cpu_affinity": affinity},
         "gpu_launches": launches_per_step * args.steps * world,
         "roofline": roof,
         "per_rank_ms": per_rank_ms,

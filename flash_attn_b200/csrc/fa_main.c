@@ -8,7 +8,11 @@
  * can be dumped to a file; the tests compare that dump with the CPU oracle (the
  * reference's in-program verfiy(), src/main.cu:254-276, is replaced by that check).
  *
- *   fa_bench --config 1|2|3|4|5 [--gpus N] [--iters I] [--warmup W] [--dump FILE] [--units U]
+ *   fa_bench --config 1|2|3|4|5 [--gpus N] [--iters I] [--warmup W] [--dump FILE] [--units U] [--check]
+ *
+ * --check verifies sampled rows of the result against a plain fp32 attention computed here on the
+ * host, and times that CPU computation (as the reference's main() does with attention_forward_cpu,
+ * src/main.cu:212-225); like the reference (src/main.cu:44, 222) it runs the launch without dropout.
  *
  * With --gpus N the (batch, head) units of configs 1-4 are cut into N contiguous slices,
  * one per device, with no communication; every device gets its own stream and the job
@@ -23,6 +27,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <time.h>
 #include <cuda_runtime_api.h>
 #include "fa_b200.h"
 
@@ -98,6 +103,48 @@ static void fill(uint16_t* dst, size_t n, uint64_t seed, uint64_t stream, float 
     }
 }
 
+
+static float from_bf16(uint16_t h) { uint32_t u = (uint32_t)h << 16; float f; memcpy(&f, &u, 4); return f; }
+static float from_fp16(uint16_t h) {
+    const uint32_t sign = ((uint32_t)h & 0x8000u) << 16, exp = (h >> 10) & 0x1F, man = h & 0x3FFu;
+    uint32_t u;
+    if (exp == 0) {
+        if (man == 0) u = sign;
+        else { int e = -1; uint32_t m = man; do { ++e; m <<= 1; } while (!(m & 0x400u)); u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13); }
+    } else if (exp == 31) u = sign | 0x7F800000u | (man << 13);
+    else u = sign | ((exp - 15 + 127) << 23) | (man << 13);
+    float f; memcpy(&f, &u, 4); return f;
+}
+/* --check: the program's own verification, the successor of the reference's attention_forward_cpu + verfiy
+ * (src/main.cu:212-225, 254-388) on sampled rows: plain fp32 attention of one query row over the unit's keys
+ * with the launch's masks and ALiBi.  Returns the output row in out[d]. */
+static void naive_row(const uint16_t* q, const uint16_t* k, const uint16_t* v, int dtype, int row, int Nk, int d,
+                      float scale, int causal, int wl, int wr, float slope, long q_pos0, float* scores, float* out) {
+    float mx = -INFINITY;
+    const long qp = q_pos0 + row;
+    for (int j = 0; j < Nk; ++j) {
+        const int masked = (causal && j > qp) || (wl >= 0 && qp - j > wl) || (wr >= 0 && j - qp > wr);
+        if (masked) { scores[j] = -INFINITY; continue; }
+        float acc = 0.0f;
+        for (int c = 0; c < d; ++c) {
+            const float a = dtype == FA_DTYPE_BF16 ? from_bf16(q[(size_t)row * d + c]) : from_fp16(q[(size_t)row * d + c]);
+            const float b = dtype == FA_DTYPE_BF16 ? from_bf16(k[(size_t)j * d + c]) : from_fp16(k[(size_t)j * d + c]);
+            acc += a * b;
+        }
+        scores[j] = acc * scale - slope * (float)labs(qp - j);
+        if (scores[j] > mx) mx = scores[j];
+    }
+    float sum = 0.0f;
+    for (int j = 0; j < Nk; ++j) { scores[j] = scores[j] == -INFINITY ? 0.0f : expf(scores[j] - mx); sum += scores[j]; }
+    for (int c = 0; c < d; ++c) out[c] = 0.0f;
+    if (sum > 0.0f)
+        for (int j = 0; j < Nk; ++j) {
+            if (scores[j] == 0.0f) continue;
+            const float p = scores[j] / sum;
+            for (int c = 0; c < d; ++c)
+                out[c] += p * (dtype == FA_DTYPE_BF16 ? from_bf16(v[(size_t)j * d + c]) : from_fp16(v[(size_t)j * d + c]));
+        }
+}
 
 /* ---- config 5: bf16 [1,32,131072,128] causal, N(0, 0.5), the sequence sharded over the devices ---- */
 typedef struct {
@@ -239,7 +286,7 @@ typedef struct {
 } shard_t;
 
 int main(int argc, char** argv) {
-    int cfg_id = 1, gpus = 1, iters = 20, warmup = 3, units_override = 0, seq = 131072;
+    int cfg_id = 1, gpus = 1, iters = 20, warmup = 3, units_override = 0, seq = 131072, check = 0;
     const char* dump = NULL;
     for (int i = 1; i < argc; ++i) {
         if (!strcmp(argv[i], "--config") && i + 1 < argc) cfg_id = atoi(argv[++i]);
@@ -249,7 +296,8 @@ int main(int argc, char** argv) {
         else if (!strcmp(argv[i], "--units") && i + 1 < argc) units_override = atoi(argv[++i]);
         else if (!strcmp(argv[i], "--dump") && i + 1 < argc) dump = argv[++i];
         else if (!strcmp(argv[i], "--seq") && i + 1 < argc) seq = atoi(argv[++i]);  /* config 5: sequence length (tests) */
-        else { fprintf(stderr, "usage: fa_bench --config 1..5 [--gpus N] [--iters I] [--warmup W] [--units U] [--dump FILE] [--seq N]\n"); return 2; }
+        else if (!strcmp(argv[i], "--check")) check = 1;
+        else { fprintf(stderr, "usage: fa_bench --config 1..5 [--gpus N] [--iters I] [--warmup W] [--units U] [--dump FILE] [--seq N] [--check]\n"); return 2; }
     }
     if (cfg_id < 1 || cfg_id > 5 || gpus < 1 || iters < 1) { fprintf(stderr, "fa_bench: bad arguments\n"); return 2; }
     if (cfg_id == 5) {
@@ -259,6 +307,7 @@ int main(int argc, char** argv) {
         return run_config5(gpus, iters, warmup, seq);
     }
     config_t c = kConfigs[cfg_id - 1];
+    if (check) c.p = 0.0f;  /* the verification has no dropout (src/main.cu:44, 222) */
     int units = c.B * c.H;
     if (units_override > 0 && units_override < units) units = units_override;  /* a prefix of the units (tests) */
     int ndev = 0;
@@ -390,9 +439,58 @@ int main(int argc, char** argv) {
         fclose(f);
     }
 
+    double check_max = -1.0, check_mean = 0.0, cpu_ms_per_row = 0.0;
+    int check_rows = 0;
+    if (check) {
+        /* sampled rows of device 0's slice: first, last, tile edges and a stride through the rest */
+        shard_t* s0 = &sh[0];
+        CHECK_CUDA(cudaSetDevice(0));
+        float* scores = (float*)malloc(sizeof(float) * (size_t)c.Nk);
+        float* want = (float*)malloc(sizeof(float) * (size_t)c.d);
+        uint16_t* got = (uint16_t*)malloc(2 * (size_t)c.d);
+        struct timespec t0, t1;
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+        check_max = 0.0;
+        double sum = 0.0;
+        const int sample_units = s0->units < 3 ? s0->units : 3;
+        for (int su = 0; su < sample_units; ++su) {
+            const int u = su == 0 ? 0 : (su == 1 ? s0->units - 1 : s0->units / 2);
+            const int src = (s0->unit0 + u) % distinct;
+            const int rows[8] = {0, c.Nq / 2, c.Nq - 1, c.Nq > 128 ? 127 : 0, c.Nq > 128 ? 128 : 0, c.Nq > 1025 ? 1024 : 0,
+                                 c.Nq > 1025 ? 1025 : 0, (int)((977u * (unsigned)(su + 1)) % (unsigned)c.Nq)};
+            for (int r = 0; r < 8; ++r) {
+                const int row = rows[r];
+                naive_row(hq + (size_t)src * q_unit, hk + (size_t)src * kv_unit, hv + (size_t)src * kv_unit, c.dtype, row, c.Nk,
+                          c.d, 1.0f / sqrtf((float)c.d), c.causal, c.wl, c.wr, c.alibi ? hslopes[s0->unit0 + u] : 0.0f,
+                          0L, scores, want);
+                CHECK_CUDA(cudaMemcpy(got, (char*)s0->o + ((size_t)u * q_unit + (size_t)row * c.d) * 2, 2 * (size_t)c.d,
+                                      cudaMemcpyDeviceToHost));
+                for (int x = 0; x < c.d; ++x) {
+                    const double e = fabs((double)(c.dtype == FA_DTYPE_BF16 ? from_bf16(got[x]) : from_fp16(got[x])) - (double)want[x]);
+                    if (e > check_max) check_max = e;
+                    sum += e;
+                }
+                ++check_rows;
+            }
+        }
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        check_mean = sum / ((double)check_rows * c.d);
+        cpu_ms_per_row = ((double)(t1.tv_sec - t0.tv_sec) * 1e3 + (double)(t1.tv_nsec - t0.tv_nsec) * 1e-6) / check_rows;
+        free(scores); free(want); free(got);
+    }
+
     printf("{\"driver\": \"fa_bench\", \"config\": \"%s\", \"units\": %d, \"n_gpus\": %d, \"iters\": %d, \"ms_per_iter\": %.6f, "
-           "\"tflops\": %.3f, \"gbs\": %.1f, \"checksum\": %.0f}\n",
+           "\"tflops\": %.3f, \"gbs\": %.1f, \"checksum\": %.0f",
            c.name, units, gpus, iters, ms_iter, flops / (ms_iter * 1e-3) / 1e12, bytes / (ms_iter * 1e-3) / 1e9, checksum);
+    if (check) {
+        /* CPU time of the whole workload, extrapolated linearly in rows from the sampled ones (1 core) */
+        const double cpu_s = cpu_ms_per_row * 1e-3 * (double)c.Nq * units;
+        printf(", \"check\": {\"rows\": %d, \"max_abs\": %.5f, \"mean_abs\": %.6f, \"pass\": %s, \"dropout\": \"off for the check\"}, "
+               "\"cpu\": {\"cores\": 1, \"ms_per_row\": %.4f, \"seconds_whole_workload_extrapolated\": %.1f}",
+               check_rows, check_max, check_mean, (check_max <= 2e-2 && check_mean <= 2e-3) ? "true" : "false", cpu_ms_per_row, cpu_s);
+    }
+    printf("}\n");
+    if (check && !(check_max <= 2e-2 && check_mean <= 2e-3)) return 3;
 
     for (int g = 0; g < gpus; ++g) if (sh[g].units) {
         cudaSetDevice(g);

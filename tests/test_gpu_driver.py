@@ -53,3 +53,28 @@ def test_driver_config4_first_units_decode():
     line, raw = _run(["--config", "4", "--units", "2", "--iters", "2"])
     _check(raw, 2, 1, 32768, 128, "bfloat16", 4)
     assert line["gbs"] > 0
+
+
+@pytest.mark.parametrize("args", [["--config", "1"], ["--config", "2", "--units", "4"], ["--config", "3", "--units", "3"],
+                                  ["--config", "4", "--units", "2"]])
+def test_driver_checks_itself(args):
+    # --check: the driver's own verification on sampled rows (plain fp32 attention in the driver, not the
+    # oracle) and its CPU timing leg, as the reference's main() has them (src/main.cu:212-225)
+    from flash_attn_b200 import build
+    exe = build.build_driver()
+    out = subprocess.run([exe] + args + ["--iters", "2", "--check"], capture_output=True, timeout=600)
+    assert out.returncode == 0, out.stderr.decode()
+    line = json.loads(out.stdout.decode().strip().splitlines()[-1])
+    assert line["check"]["pass"] is True and line["check"]["rows"] >= 8
+    assert line["cpu"]["ms_per_row"] > 0
+
+
+def test_driver_config5_ring_on_one_gpu():
+    # the ring through fa_ring_fwd with one rank (no exchange), at a shortened sequence
+    from flash_attn_b200 import build
+    exe = build.build_driver()
+    out = subprocess.run([exe, "--config", "5", "--gpus", "1", "--iters", "1", "--warmup", "1", "--seq", "16384"],
+                         capture_output=True, timeout=600)
+    assert out.returncode == 0, out.stderr.decode()
+    line = json.loads(out.stdout.decode().strip().splitlines()[-1])
+    assert line["n_gpus"] == 1 and line["tflops"] > 0 and line["chunk_rows"] == 8192
