@@ -214,7 +214,10 @@ int fa_launch_reference_params(const fa_ref_kernel_params* param, int heads, int
  * The call itself allocates nothing and calls no allocating routine.  The first
  * call on each device looks up the array's device address
  * (cudaGetSymbolAddress) and keeps it; make that first call outside any stream
- * capture.  All calls on a device share the one array, which keeps whatever
+ * capture, and make it at start-up: under the runtime's lazy module loading it is
+ * this lookup that loads the module image on the device, the 32 MiB included, so
+ * it can fail with FA_ERR_CUDA once another allocator holds all of the device's
+ * memory.  The address kept does not survive cudaDeviceReset.  All calls on a device share the one array, which keeps whatever
  * the last call left: nothing in it needs clearing (every partial that is read
  * is written first by the same call), but two calls that overlap on the GPU --
  * different streams, or different host threads -- race on it and give wrong

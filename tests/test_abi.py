@@ -55,6 +55,36 @@ def test_struct_layout_matches_the_header():
         assert getattr(_lib.FwdParams, f).offset == int(off), f
 
 
+def test_ring_struct_layout_matches_the_header():
+    from flash_attn_b200 import _lib
+    fields = [f[0] for f in _lib.RingParams._fields_]
+    src = '#include <stdio.h>\n#include <stddef.h>\n#include "fa_b200.h"\nint main(void){printf("%zu", sizeof(fa_ring_params));\n'
+    for f in fields:
+        src += f'printf(" %zu", offsetof(fa_ring_params, {f}));\n'
+    src += "return 0;}\n"
+    with tempfile.TemporaryDirectory() as tmp:
+        c = os.path.join(tmp, "layout.c")
+        open(c, "w").write(src)
+        exe = os.path.join(tmp, "layout")
+        subprocess.check_call(["/usr/bin/gcc" if os.path.exists("/usr/bin/gcc") else "gcc", "-std=c99", "-I",
+                               os.path.join(ROOT, "include"), c, "-o", exe])
+        out = subprocess.check_output([exe]).decode().split()
+    assert int(out[0]) == ctypes.sizeof(_lib.RingParams)
+    for f, off in zip(fields, out[1:]):
+        assert getattr(_lib.RingParams, f).offset == int(off), f
+
+
+def test_ring_entry_points_reject_bad_arguments(lib):
+    from flash_attn_b200 import _lib
+    p = _lib.RingParams()
+    assert lib.fa_ring_message_bytes(ctypes.byref(p)) == 0
+    assert lib.fa_ring_fwd(ctypes.byref(p)) == -1  # world = 0
+    p.world, p.rank = 2, 0
+    assert lib.fa_ring_fwd(ctypes.byref(p)) == -1  # no communicator, no buffers
+    p.batch, p.heads, p.chunk_rows, p.head_dim, p.dtype = 1, 32, 8192, 128, _lib.FA_DTYPE_BF16
+    assert lib.fa_ring_message_bytes(ctypes.byref(p)) == 4 * 32 * 8192 * 128 * 2  # 268 MB per ring step at 8 GPUs
+
+
 def test_split_policy_matches_reference_table(lib, golden_dir):
     t = json.load(open(os.path.join(golden_dir, "num_splits_heuristic.json")))
     for a, b, c, d, e, want in t["rows"]:
