@@ -612,9 +612,17 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
             const bool tile_masked = tile_masked_pre;
             if (tile_masked) {
+                // (two passes: a causal diagonal, the common case, needs only the upper bound)
+                if (__any_sync(0xffffffffu, c_hi < kTile - 1)) {
 #pragma unroll
-                for (int c = 0; c < 128; ++c)
-                    if (c < c_lo || c > c_hi) s[c] = -INFINITY;
+                    for (int c = 0; c < 128; ++c)
+                        if (c > c_hi) s[c] = -INFINITY;
+                }
+                if (__any_sync(0xffffffffu, c_lo > 0)) {
+#pragma unroll
+                    for (int c = 0; c < 128; ++c)
+                        if (c < c_lo) s[c] = -INFINITY;
+                }
             }
 
             // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
@@ -692,10 +700,12 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
             const float2 neg_m2 = make_float2(neg_m, neg_m);
             const float2 scale22 = make_float2(scale2, scale2);
-            // On tiles without masked elements (every score finite, so no argument is -inf) pairs
-            // kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.
-            auto exp_tile = [&](auto poly_tag) {
+            // Pairs kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.  The
+            // polynomial needs finite arguments: on tiles with masked (-inf) scores its results for those
+            // elements are replaced by 0 (MUFU gives 0 by itself).
+            auto exp_tile = [&](auto poly_tag, auto guard_tag) {
                 constexpr int kPolyFrom = decltype(poly_tag)::value;
+                constexpr bool kGuard = decltype(guard_tag)::value;  // the tile has masked (-inf) scores
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {  // quarters of 32 columns
                     uint32_t pr[16];
@@ -715,6 +725,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             float2 p;
                             if (q >= kPolyFrom) {
                                 p = poly_exp2_pair(x);
+                                if constexpr (kGuard) {
+                                    // the polynomial gives 2^-126, not 0, for a masked score
+                                    if (s[col] == -INFINITY) p.x = 0.0f;
+                                    if (s[col + 1] == -INFINITY) p.y = 0.0f;
+                                }
                             } else {
                                 p.x = fast_exp2(x.x);
                                 p.y = fast_exp2(x.y);
@@ -734,8 +749,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
             };
-            if (tile_masked) exp_tile(std::integral_constant<int, 4>{});
-            else exp_tile(std::integral_constant<int, kPolyPairsFrom>{});
+            if (tile_masked) exp_tile(std::integral_constant<int, kPolyPairsFrom>{}, std::true_type{});
+            else exp_tile(std::integral_constant<int, kPolyPairsFrom>{}, std::false_type{});
             FA_TR(6);
             l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();
