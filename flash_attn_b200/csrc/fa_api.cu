@@ -502,8 +502,12 @@ int fa_fwd_host(const fa_fwd_params* p) {
     const size_t kv_unit = static_cast<size_t>(p->seqlen_k) * p->head_dim * esz;
     const size_t o_unit = static_cast<size_t>(p->seqlen_q) * p->head_dim * osz;
     const size_t lse_unit = static_cast<size_t>(p->seqlen_q) * sizeof(float);
-    // slices of units, double-buffered so copies in one stream overlap work in the other
-    const long long slices = std::min<long long>(kunits, 8);
+    // slices of units, double-buffered so copies in one stream overlap work in the other.  The count follows
+    // the transfer size: about 32 MB of host-to-device traffic per slice (long enough to run the link at its
+    // rate, short enough that the first kernel starts early and the last copy back is short), 2 to 16 slices.
+    const size_t h2d_total = static_cast<size_t>(units) * q_unit + 2 * static_cast<size_t>(kunits) * kv_unit;
+    const long long by_size = static_cast<long long>(h2d_total / (32u << 20));
+    const long long slices = std::min<long long>(kunits, std::max<long long>(2, std::min<long long>(16, by_size)));
     const long long per_k = (kunits + slices - 1) / slices;
     const long long per = per_k * group;
     auto align = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
