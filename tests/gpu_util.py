@@ -20,7 +20,7 @@ def to_dev(x, dtype_name):
 
 def run_case(B, H, Nq, Nk, d, dtype="bfloat16", seed=0, sigma=1.0, scale=None, causal=False, window=(-1, -1),
              alibi=False, p_dropout=0.0, drop_seed=42, offset=0, num_splits=1, q_pos0=0, k_pos0=0,
-             out_dtype=None, rows=None, heads_k=None, host=False):
+             out_dtype=None, rows=None, heads_k=None, host=False, launch_index=0):
     """Returns dict with errors of the CUDA result against the oracle.  heads_k < H runs
     grouped-query attention (the oracle sees K/V repeated per query head); host=True goes
     through the host-buffer entry point."""
@@ -46,7 +46,7 @@ def run_case(B, H, Nq, Nk, d, dtype="bfloat16", seed=0, sigma=1.0, scale=None, c
             to_dev(q, dtype), to_dev(k_dev, dtype), to_dev(v_dev, dtype), softmax_scale=scale, causal=causal,
             window=window, alibi_slopes=None if slopes is None else torch.from_numpy(slopes), p_dropout=p_dropout,
             seed=drop_seed, offset=offset, num_splits=num_splits, q_pos0=q_pos0, k_pos0=k_pos0, out_dtype=out_dtype,
-            status=status)
+            status=status, launch_index=launch_index)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, f"device wait timed out: status {int(status.item())}"
     # the split count the library really used decides the dropout stream geometry
@@ -55,7 +55,8 @@ def run_case(B, H, Nq, Nk, d, dtype="bfloat16", seed=0, sigma=1.0, scale=None, c
         used_splits = min(max(1, num_splits), (Nk + 127) // 128)
     want_o, want_lse = oracle_lib.forward(q, k, v, scale, causal=causal, window=window, alibi_slopes=slopes,
                                           p_dropout=p_dropout, seed=drop_seed, offset=offset,
-                                          dropout_splits=used_splits, q_pos0=q_pos0, k_pos0=k_pos0, rows=rows)
+                                          dropout_splits=used_splits, q_pos0=q_pos0, k_pos0=k_pos0, rows=rows,
+                                          launch_index=launch_index)
     got_o = o.float().cpu().numpy()
     got_lse = lse.cpu().numpy()
     if rows is not None:
