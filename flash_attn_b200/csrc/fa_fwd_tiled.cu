@@ -75,6 +75,8 @@ namespace {
 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by > 2^8
 constexpr int kPolyPairsFrom = 3;  // of every 4 column pairs, pairs >= this use the polynomial exp2
+constexpr int kKeepChunk = 2;              // KV tiles whose dropout keep bits are handed over at a time (one Philox pass)
+constexpr int kKeepRing = 2 * kKeepChunk;  // tiles the keep-bit table holds
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -88,7 +90,7 @@ struct Cfg {
     // forever, hence the static_assert.
     // ptxas allots 168 registers per thread under __launch_bounds__(384, 1) and 128 under (256, 2)
     static constexpr int kRegsLaunch = NQ == 2 ? 168 : 128;
-    static constexpr int kRegsHelper = NQ == 2 ? 48 : 40;     // producer / MMA warpgroup after the hand-over
+    static constexpr int kRegsHelper = NQ == 2 ? 56 : 48;     // producer / MMA warpgroup after the hand-over
     static constexpr int kRegsSoftmax = NQ == 2 ? 224 : 208;  // softmax warpgroups after the hand-over
     static_assert(NQ * 128 * kRegsSoftmax + 128 * kRegsHelper <= kThreads * kRegsLaunch,
                   "register hand-over exceeds the CTA's allocation");
@@ -105,7 +107,10 @@ struct Cfg {
     static constexpr int kSmemV = kSmemK + kStages * kTileBytes;
     static constexpr int kSmemBar = kSmemV + kStages * kTileBytes;
     static constexpr int kNumBars = 1 + 2 * NQ + 4 * kStages;
-    static constexpr int kSmemBytes = kSmemBar + 8 * kNumBars + 16 + 1024;  // + alignment slack
+    // dropout keep bits, written by a helper warp per query tile: [NQ][2 row halves][kKeepRing tiles] words
+    static constexpr int kSmemKeep = kSmemBar + 8 * kNumBars + 16;
+    static constexpr int kSmemBytes = kSmemKeep + NQ * kKeepRing * 2 * 4 + 1024;  // + alignment slack
+    static constexpr int kKeepWarp0 = NQ * 4 + 2;  // the helper warp of query tile i is kKeepWarp0 + i
 };
 
 struct TileRange {
@@ -199,7 +204,11 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
 // cycles, while a poll of a shared-memory mbarrier took several hundred whenever the tensor
 // pipe was streaming operands.  A named barrier cannot time out, so a softmax warp whose
 // mbarrier wait gave up keeps walking its tile loop and posts every arrival it owes.
-constexpr int kPBarrierThreads = 160;  // 128 softmax threads + the MMA warp
+constexpr int kPBarrierThreads = 160;  // 128 softmax threads + the MMA warp (or + a keep-bit helper warp)
+// Barrier ids: 0 = __syncthreads; 1 + 2i, 2 + 2i = P of query tile i (first part, complete);
+// 5 + 2i + h = keep bits of half-ring h of query tile i written; 9 + 2i + h = that half-ring read.
+__device__ __forceinline__ int keep_full_id(int qi, int h) { return 5 + 2 * qi + h; }
+__device__ __forceinline__ int keep_empty_id(int qi, int h) { return 9 + 2 * qi + h; }
 __device__ __forceinline__ void named_arrive(int id) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "n"(kPBarrierThreads) : "memory");
 }
@@ -297,6 +306,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t bar_v_empty = bar_v_full + 8 * C::kStages;    // [kStages]
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kSmemBar + 8 * C::kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kSmemBar + 8 * C::kNumBars + 4);
+    volatile uint32_t* keep_tab = reinterpret_cast<volatile uint32_t*>(smem_gen + C::kSmemKeep);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -405,6 +415,44 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (n_union > 0) {
             tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
             tmem_relinquish();
+        }
+    }
+    // Dropout keep bits.  One otherwise idle warp per query tile evaluates the Philox blocks of that
+    // tile's stream (src/flash_forward.h:50-54,221-237) for the whole softmax warpgroup, whose four
+    // warps all need the same 64 draws per KV tile: lanes 0-15 take one KV tile of a chunk, lanes
+    // 16-31 the next (lane & 15 = 2*i + row-half: draws 8*i + 4*half + {0..3}), the eight blocks of a
+    // row half are OR-ed into one word (bit 4*i + w) by three shuffles, and the words go to a ring of
+    // kKeepRing tiles in shared memory, handed over a chunk at a time over named barriers.  The first
+    // chunk is written here, before the CTA-wide sync, so that it is there when the first S arrives.
+    const int keep_qi = warp - C::kKeepWarp0;
+    int keep_tiles = 0;
+    unsigned long long keep_subseq = 0, keep_first = 0;
+    auto keep_chunk = [&](int chunk) {
+        const int j = chunk * kKeepChunk + (lane >> 4);  // position in the walk (last KV tile first)
+        uint32_t v = 0;
+        if (j < keep_tiles)
+            v = philox_keep4(a.drop, keep_subseq,
+                             keep_first + 64ull * static_cast<unsigned long long>(keep_tiles - 1 - j) +
+                                 4ull * static_cast<unsigned long long>(lane & 15))
+                << (4 * ((lane & 15) >> 1));
+        v |= __shfl_xor_sync(0xffffffffu, v, 2);
+        v |= __shfl_xor_sync(0xffffffffu, v, 4);
+        v |= __shfl_xor_sync(0xffffffffu, v, 8);
+        if ((lane & 14) == 0 && j < keep_tiles)
+            keep_tab[(keep_qi * 2 + (lane & 1)) * kKeepRing + (j & (kKeepRing - 1))] = v;
+        __threadfence_block();
+        named_arrive(keep_full_id(keep_qi, chunk & 1));
+    };
+    if constexpr (kDropout) {
+        if (warp >= C::kKeepWarp0 && warp < C::kKeepWarp0 + NQ) {
+            const TileRange kr = (keep_qi == 0) ? range[0] : range[NQ - 1];
+            keep_tiles = kr.hi - kr.lo;
+            keep_subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
+                          static_cast<unsigned long long>((qb * NQ + keep_qi) * a.num_splits + split);
+            keep_first = continuation(a.drop, keep_tiles);
+            FA_TR(40);
+            if (keep_tiles > 0) keep_chunk(0);
+            FA_TR(41);
         }
     }
     grid_dep_wait();  // every thread, before its first global access (the producer lane has passed it already)
@@ -532,6 +580,13 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
             } while (false);
+        } else if (kDropout && warp >= C::kKeepWarp0 && warp < C::kKeepWarp0 + NQ) {
+            // ======================= dropout keep bits ==============================
+            // (the first chunk was written before the CTA-wide sync)
+            for (int chunk = 1; chunk * kKeepChunk < keep_tiles; ++chunk) {
+                if (chunk >= 2) named_sync(keep_empty_id(keep_qi, chunk & 1));  // the softmax group has read chunk - 2
+                keep_chunk(chunk);
+            }
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsSoftmax));
@@ -556,27 +611,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
         // every unmasked key lies at or before the query: |q - k| = q - k
         const bool keys_not_after = a.is_causal || a.window_right == 0;
-        unsigned long long subseq = 0;
-        if constexpr (kDropout)
-            subseq = (a.drop.unit0 + unit) * static_cast<unsigned long long>(a.tr * a.num_splits) +
-                     static_cast<unsigned long long>(rb * a.num_splits + split);
         const float scale2 = a.scale_log2;
-        // Dropout keep bits of this row for KV tile j of this query tile: bit 2*g + w <-> columns
-        // 8g..8g+7 of parity w.  Lanes 0-15 evaluate one Philox block each (lane = 2*i + row-half:
-        // draws 8*i + 4*half + {0..3}); a row gathers the eight blocks of its half.  Computed one
-        // tile ahead, while the warp would otherwise wait for S.
-        const unsigned long long drop_cont = kDropout ? continuation(a.drop, n_tiles) : 0ull;
-        auto tile_keep_bits = [&](int j) -> uint32_t {
-            if constexpr (!kDropout) return 0xffffffffu;
-            uint32_t mine = 0;
-            if (lane < 16) mine = philox_keep4(a.drop, subseq, drop_cont + 64ull * static_cast<unsigned long long>(j) + 4ull * lane);
-            const int half = (lane >> 3) & 1;
-            uint32_t bits = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) bits |= __shfl_sync(0xffffffffu, mine, 2 * i + half) << (4 * i);
-            return bits;
-        };
-        uint32_t keep_next = n_tiles > 0 ? tile_keep_bits(n_tiles - 1) : 0u;  // argument: tile index from the first KV tile
+        // Dropout keep bits of this row for the KV tile at hand: bit 2*g + w <-> columns 8g..8g+7 of
+        // parity w; read from the table the keep-bit helper warp of this query tile fills.
+        uint32_t keep_bits = 0xffffffffu, keep_odd = 0xffffffffu;
+        static_assert(kKeepChunk == 2, "the softmax loop reads a chunk's two words at once");
 
         for (int j = 0; j < n_tiles; ++j) {
             const int cb = t_lo + n_tiles - 1 - j;  // from the last KV tile of this query tile to the first
@@ -587,6 +626,21 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             if (a.window_right >= 0) c_hi = static_cast<int>(min(static_cast<long long>(c_hi), qpos + a.window_right - kbase));
             if (a.window_left >= 0) c_lo = static_cast<int>(max(0LL, min(qpos - a.window_left - kbase, 128LL)));
             const bool tile_masked_pre = __any_sync(0xffffffffu, c_lo > 0 || c_hi < kTile - 1);
+            if constexpr (kDropout) {
+                if ((j & 1) == 0) {
+                    const int chunk = j / kKeepChunk;
+                    // the chunk before this one has been read: its half of the ring may be refilled
+                    if (chunk >= 1 && (chunk + 1) * kKeepChunk < n_tiles) named_arrive(keep_empty_id(qi, (chunk - 1) & 1));
+                    named_sync(keep_full_id(qi, chunk & 1));
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
+                                 : "=r"(keep_bits), "=r"(keep_odd)
+                                 : "r"(smem_base + C::kSmemKeep +
+                                       4u * static_cast<uint32_t>((qi * 2 + ((lane >> 3) & 1)) * kKeepRing + (chunk & 1) * kKeepChunk))
+                                 : "memory");
+                } else {
+                    keep_bits = keep_odd;
+                }
+            }
             FA_TR(1);
             if (fail != 0 || !mbar_wait_warp(my_s_full, j & 1, abort_flag)) {
                 // a wait gave up: keep the barrier protocol alive (the MMA warp counts on two
@@ -693,7 +747,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             l_sum *= (m_new != m_ref) ? factor : 1.0f;
             m_ref = m_new;
             const float neg_m = (m_ref == -INFINITY) ? 0.0f : -m_ref;
-            const uint32_t keep_bits = keep_next;
             FA_TR(5);
 
             // P = exp2(s*scale - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
@@ -757,7 +810,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             tc_fence_before_sync();
             named_arrive(2 + 2 * qi);
             FA_TR(7);
-            if (j + 1 < n_tiles) keep_next = tile_keep_bits(n_tiles - 2 - j);
         }
 
         // ---- epilogue: normalise and write O, LSE --------------------------------
