@@ -320,6 +320,22 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // waiting for the kernel in front of it; no global memory is touched before grid_dep_wait().
     grid_dep_launch_dependents();
 
+    // The producer warp initialises every barrier (one per lane, a single instruction) and asks for
+    // the tensor maps before any index arithmetic: neither depends on which tiles the CTA owns, and
+    // the maps are kernel parameters, not memory of the kernel in front.
+    if (warp == C::kProducerWarp) {
+        if (lane < C::kNumBars) mbar_init(bar0 + 8 * lane, 1);
+        if (lane == 0) {
+            *abort_flag = 0;
+            tma_prefetch_desc(&tmap_q);
+            tma_prefetch_desc(&tmap_k);
+            tma_prefetch_desc(&tmap_v);
+            if (a.o_tma) tma_prefetch_desc(&tmap_o);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_fence_init();
+    }
+
     // ---- which query tiles does this CTA own ------------------------------------
     const int trq = (a.tr + NQ - 1) / NQ;  // query blocks of NQ tiles
     // CTA order: groups of unit_group units; inside a group all units' first query block, then
@@ -340,11 +356,38 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     int qb = static_cast<int>(qb_raw);
     if (a.is_causal) qb = trq - 1 - qb;  // heaviest query blocks first
     FA_TR(94);
+    // The producer lane puts the Q tiles in flight as soon as it knows which they are (a tile whose
+    // key range then turns out empty is loaded for nothing: fully masked blocks only), the K/V tiles
+    // once the ranges are known; the HBM latency of these first loads overlaps the rest of the set-up,
+    // the TMEM allocation and the CTA-wide synchronisation instead of following them.
+    // Every box of these first loads is issued by a lane of its own (one instruction puts them all in
+    // flight: a single thread needs 100-200 cycles per TMA instruction).
+    int q_tiles = 0;  // Q tiles in flight (producer warp only)
+    if (warp == C::kProducerWarp) {
+        grid_dep_wait();
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) q_tiles += (qb * NQ + i < a.tr) ? 1 : 0;
+        if (lane == 0 && q_tiles > 0) mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
+        if (lane < NQ * C::kBoxes) {
+            const int i = lane / C::kBoxes, b = lane % C::kBoxes;
+            if (qb * NQ + i < a.tr)
+                tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
+                            (qb * NQ + i) * kTile, unit);
+        }
+    }
+    // (the NQ ranges are worked out side by side on lanes 0..NQ-1 and handed round)
     TileRange range[NQ];
+    {
+        const TileRange mine = kv_tile_range(a, qb * NQ + (lane & (NQ - 1)), split);
+#pragma unroll
+        for (int i = 0; i < NQ; ++i) {
+            range[i].lo = NQ == 1 ? mine.lo : __shfl_sync(0xffffffffu, mine.lo, i);
+            range[i].hi = NQ == 1 ? mine.hi : __shfl_sync(0xffffffffu, mine.hi, i);
+        }
+    }
     int lo = 0x7fffffff, hi = 0;
 #pragma unroll
     for (int i = 0; i < NQ; ++i) {
-        range[i] = kv_tile_range(a, qb * NQ + i, split);
         if (range[i].hi > range[i].lo) {
             lo = min(lo, range[i].lo);
             hi = max(hi, range[i].hi);
@@ -354,64 +397,25 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     FA_TR(95);
 
     // ---- set-up ----------------------------------------------------------------
-    // The producer lane initialises the barriers and immediately puts the Q tiles and the first
-    // ring-full of K/V tiles in flight, so that the HBM latency of these first loads overlaps the
-    // TMEM allocation and the CTA-wide synchronisation instead of following them.
-    int prefilled = 0;  // K/V tiles whose loads were issued during set-up (producer lane only)
-    if (warp == C::kProducerWarp && lane == 0) {
-        *abort_flag = 0;
-        mbar_init(bar_q_full, 1);
-        for (int s = 0; s < C::kStages; ++s) {
-            mbar_init(bar_k_full + 8 * s, 1);
-            mbar_init(bar_k_empty + 8 * s, 1);
-            mbar_init(bar_v_full + 8 * s, 1);
-            mbar_init(bar_v_empty + 8 * s, 1);
-        }
-        mbar_fence_init();
-        grid_dep_wait();
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
-        if (a.o_tma) tma_prefetch_desc(&tmap_o);
+    int prefilled = 0;  // K/V tiles whose loads were issued during set-up (producer warp only)
+    if (warp == C::kProducerWarp) {
         if (n_union > 0) {
-            int q_tiles = 0;
-#pragma unroll
-            for (int i = 0; i < NQ; ++i) q_tiles += (range[i].hi > range[i].lo) ? 1 : 0;
-            mbar_expect_tx(bar_q_full, q_tiles * C::kTileBytes);
-#pragma unroll
-            for (int i = 0; i < NQ; ++i) {
-                if (range[i].hi > range[i].lo) {
-#pragma unroll
-                    for (int b = 0; b < C::kBoxes; ++b)
-                        tma_load_3d(sQ + i * C::kTileBytes + b * (kTile * 128), &tmap_q, bar_q_full, b * 64,
-                                    (qb * NQ + i) * kTile, unit);
-                }
-            }
             prefilled = min(C::kStages, n_union);
-            for (int t = 0; t < prefilled; ++t) {  // the ring is empty: no waits
-                if (FA_TEST_SKIPS(t)) continue;
+            // lane = (tile t of the ring, K or V, box): the ring is empty, no waits
+            const int t = lane / (2 * C::kBoxes), is_v = (lane / C::kBoxes) & 1, b = lane % C::kBoxes;
+            if (t < prefilled && !FA_TEST_SKIPS(t)) {
                 const int row = (hi - 1 - t) * kTile;  // KV tiles are walked from the last to the first
-                mbar_expect_tx(bar_k_full + 8 * t, C::kTileBytes);
-#pragma unroll
-                for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sK + t * C::kTileBytes + b * (kTile * 128), &tmap_k, bar_k_full + 8 * t, b * 64, row, kv_unit);
-                mbar_expect_tx(bar_v_full + 8 * t, C::kTileBytes);
-#pragma unroll
-                for (int b = 0; b < C::kBoxes; ++b)
-                    tma_load_3d(sV + t * C::kTileBytes + b * (kTile * 128), &tmap_v, bar_v_full + 8 * t, b * 64, row, kv_unit);
+                const uint32_t bar = (is_v ? bar_v_full : bar_k_full) + 8 * t;
+                if (b == 0) mbar_expect_tx(bar, C::kTileBytes);
+                tma_load_3d((is_v ? sV : sK) + t * C::kTileBytes + b * (kTile * 128), is_v ? &tmap_v : &tmap_k, bar,
+                            b * 64, row, kv_unit);
             }
+        } else if (lane == 0 && q_tiles > 0) {
+            // nothing to do for this CTA after all: its Q tiles must land before the CTA may exit
+            (void)mbar_wait(bar_q_full, 0, abort_flag);
         }
     }
     if (warp == C::kMmaWarp) {
-        // (the barriers the producer lane does not need for its first loads are initialised here, off its path)
-        if (lane == 0) {
-            for (int i = 0; i < NQ; ++i) {
-                mbar_init(bar_s_full + 8 * i, 1);
-                mbar_init(bar_o_full + 8 * i, 1);
-            }
-            mbar_fence_init();
-        }
-        __syncwarp();
         if (n_union > 0) {
             tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), C::kTmemCols);
             tmem_relinquish();
