@@ -186,6 +186,13 @@ __device__ __forceinline__ float2 poly_exp2_pair(float2 x) {
     return p;
 }
 
+// Byte permute whose selector nibbles 8 + n give 0xff or 0x00 by the sign bit of byte n of x.
+__device__ __forceinline__ uint32_t prmt_sign(uint32_t x, uint32_t selector) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %1, %2;" : "=r"(r) : "r"(x), "r"(selector));
+    return r;
+}
+
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -425,7 +432,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     // tile's stream (src/flash_forward.h:50-54,221-237) for the whole softmax warpgroup, whose four
     // warps all need the same 64 draws per KV tile: lanes 0-15 take one KV tile of a chunk, lanes
     // 16-31 the next (lane & 15 = 2*i + row-half: draws 8*i + 4*half + {0..3}), the eight blocks of a
-    // row half are OR-ed into one word (bit 4*i + w) by three shuffles, and the words go to a ring of
+    // row half are OR-ed into one word by three shuffles, and the words go to a ring of
     // kKeepRing tiles in shared memory, handed over a chunk at a time over named barriers.  The first
     // chunk is written here, before the CTA-wide sync, so that it is there when the first S arrives.
     const int keep_qi = warp - C::kKeepWarp0;
@@ -434,11 +441,15 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     auto keep_chunk = [&](int chunk) {
         const int j = chunk * kKeepChunk + (lane >> 4);  // position in the walk (last KV tile first)
         uint32_t v = 0;
-        if (j < keep_tiles)
-            v = philox_keep4(a.drop, keep_subseq,
-                             keep_first + 64ull * static_cast<unsigned long long>(keep_tiles - 1 - j) +
-                                 4ull * static_cast<unsigned long long>(lane & 15))
-                << (4 * ((lane & 15) >> 1));
+        if (j < keep_tiles) {
+            const uint32_t k4 = philox_keep4(a.drop, keep_subseq,
+                                             keep_first + 64ull * static_cast<unsigned long long>(keep_tiles - 1 - j) +
+                                                 4ull * static_cast<unsigned long long>(lane & 15));
+            // draw w of block i decides columns 16*i + 8*(w/2) + {0..7} of parity w%2: its keep bit goes
+            // to bit 8*w + 7 - i, so that after a left shift by i the four bits of block i are the sign
+            // bits of the word's four bytes (see the byte permutes of the softmax loop)
+            v = ((k4 & 1u) | ((k4 & 2u) << 7) | ((k4 & 4u) << 14) | ((k4 & 8u) << 21)) << (7 - ((lane & 15) >> 1));
+        }
         v |= __shfl_xor_sync(0xffffffffu, v, 2);
         v |= __shfl_xor_sync(0xffffffffu, v, 4);
         v |= __shfl_xor_sync(0xffffffffu, v, 8);
@@ -616,8 +627,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // every unmasked key lies at or before the query: |q - k| = q - k
         const bool keys_not_after = a.is_causal || a.window_right == 0;
         const float scale2 = a.scale_log2;
-        // Dropout keep bits of this row for the KV tile at hand: bit 2*g + w <-> columns 8g..8g+7 of
-        // parity w; read from the table the keep-bit helper warp of this query tile fills.
+        // Dropout keep bits of this row for the KV tile at hand: bit 8*(2*(g%2) + w) + 7 - g/2 <-> columns
+        // 8g..8g+7 of parity w; read from the table the keep-bit helper warp of this query tile fills.
         uint32_t keep_bits = 0xffffffffu, keep_odd = 0xffffffffu;
         static_assert(kKeepChunk == 2, "the softmax loop reads a chunk's two words at once");
 
@@ -770,8 +781,9 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     for (int g = 0; g < 4; ++g) {  // 8 columns = 4 packed pairs share one dropout mask word
                         uint32_t msk = 0xffffffffu;
                         if constexpr (kDropout) {
-                            const uint32_t two = (keep_bits >> (2 * (c * 4 + g))) & 3u;
-                            msk = __byte_perm(0u - (two & 1u), 0u - (two >> 1), 0x7610);
+                            // sign-replicating byte permute: bytes 0-1 of the mask from the sign of one byte of
+                            // the shifted keep word (even columns), bytes 2-3 from the next (odd columns)
+                            msk = prmt_sign(keep_bits << (c * 2 + (g >> 1)), (g & 1) ? 0xbbaau : 0x9988u);
                         }
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
