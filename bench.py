@@ -294,7 +294,7 @@ def run_reference_arm(args):
         return 0
     w = WORKLOADS[args.workload]
     if w["Nq"] != w["Nk"]:
-        print(json.dumps({"impl": "reference", "unavailable": "the reference CPU attention has a single sequence length; "
+        emit(json.dumps({"impl": "reference", "unavailable": "the reference CPU attention has a single sequence length; "
                           "this workload has seqlen_q != seqlen_k"}))
         return 0
     cores = os.cpu_count() or 1
@@ -311,7 +311,7 @@ def run_reference_arm(args):
         "e2e": {"value": r["tflops"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
     return 0
 
 
@@ -522,11 +522,32 @@ def run_c5(torch, fa, args, w, flops, peaks, rank, world, dev, dist, barrier, ma
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     return 0
 
 
+_RESULT_OUT = None
+
+
+def keep_stdout_for_the_result():
+    """The process's stdout carries the one JSON line and nothing else: file descriptor 1 is pointed
+    at stderr for everything that runs from here on (NCCL prints its version banner to stdout, torchrun
+    and other libraries may print too) and the original is kept for emit()."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(text):
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(text + "\n")
+    out.flush()
+
+
 def main():
+    keep_stdout_for_the_result()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None, help="default: 2000 (c2), 200 (c3), 50 (c4), 5 (c5)")
@@ -556,8 +577,7 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"  # keeps NCCL's version banner off stdout: rank 0 prints one JSON line
+
     if world != args.gpus and world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
@@ -787,7 +807,7 @@ def main():
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        print(json.dumps(line))
+        emit(json.dumps(line))
     return 0
 
 
