@@ -162,7 +162,12 @@ static void* ring_thread(void* arg) {
     const size_t head_elems = (size_t)t->chunk * t->d, chunk_elems = head_elems * t->heads;
     cudaStream_t compute, comm;
     cudaEvent_t e0, e1;
-    if (cudaStreamCreate(&compute) != cudaSuccess || cudaStreamCreate(&comm) != cudaSuccess ||
+    /* the exchange gets the highest stream priority: its few CTAs are then placed as soon as an SM
+       frees up, instead of queueing behind the thousand CTAs of the attention launch it overlaps */
+    int prio_least = 0, prio_greatest = 0;
+    if (cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest) != cudaSuccess) return NULL;
+    if (cudaStreamCreate(&compute) != cudaSuccess ||
+        cudaStreamCreateWithPriority(&comm, cudaStreamNonBlocking, prio_greatest) != cudaSuccess ||
         cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return NULL;
     fa_ring_params p;
     memset(&p, 0, sizeof(p));

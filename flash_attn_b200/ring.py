@@ -255,7 +255,9 @@ def ring_attention_forward_c(q, k, v, comm, rank, world, softmax_scale=None, cau
     msgs = _scratch(("c_msg",) + key, lambda: [torch.empty(nbytes, device=dev, dtype=torch.uint8) for _ in range(2)])
     p.message[0], p.message[1] = msgs[0].data_ptr(), msgs[1].data_ptr()
     if dev not in _comm_streams:
-        _comm_streams[dev] = torch.cuda.Stream(device=dev)
+        # highest priority: the exchange's few CTAs are placed as soon as an SM frees up instead of
+        # queueing behind the attention launch they overlap
+        _comm_streams[dev] = torch.cuda.Stream(device=dev, priority=-1)
     with torch.cuda.device(dev):
         cur = torch.cuda.current_stream(dev)
         p.compute_stream = cur.cuda_stream

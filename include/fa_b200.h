@@ -259,7 +259,11 @@ typedef struct fa_ring_params {
     float* accum_o[2];        /* device fp32, like q: running results (scratch; contents on return undefined) */
     float* accum_lse[2];      /* device fp32 [batch, heads, chunk_rows] */
     void* compute_stream;     /* cudaStream_t of the forward launches */
-    void* comm_stream;        /* cudaStream_t of the exchange; must differ from compute_stream when world > 1 */
+    void* comm_stream;        /* cudaStream_t of the exchange; must differ from compute_stream when world > 1.
+                                 Create it with the device's greatest stream priority
+                                 (cudaStreamCreateWithPriority): an attention launch keeps every SM busy with
+                                 a long queue of CTAs, and the exchange's CTAs overlap it only if they are
+                                 placed ahead of that queue when an SM frees up */
     int* status;              /* as in fa_fwd_params */
 } fa_ring_params;
 int fa_ring_fwd(const fa_ring_params* p);

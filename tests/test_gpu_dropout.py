@@ -57,7 +57,9 @@ def _mask_applied_by_forward(B, H, N, d, p, seed, dtype, **kw):
     v[:, :, idx, idx % 128] = (2.0 ** (idx // 128)).float()
     o, _ = fa.flash_attn_forward(q, k, v.to(dtype), softmax_scale=1.0, p_dropout=p, seed=seed,
                                  out_dtype=torch.float32, **kw)
-    code = torch.round(o * (N * (1.0 - np.float32(p).item()))).to(torch.int64)  # [B,H,N,128]
+    # keys a row attends to: all N, or with a causal mask those up to the row itself
+    visible = (idx + 1).double() if kw.get("causal") else torch.full((N,), float(N), device="cuda", dtype=torch.float64)
+    code = torch.round(o.double() * (visible * (1.0 - np.float32(p).item()))[None, None, :, None]).to(torch.int64)  # [B,H,N,128]
     keep = torch.zeros(B, H, N, tiles * 128, dtype=torch.uint8, device="cuda")
     for t in range(tiles):
         keep[..., t * 128:(t + 1) * 128] = ((code >> t) & 1).to(torch.uint8)
@@ -70,6 +72,21 @@ def test_forward_kernel_applies_exactly_the_reference_mask(dtype):
     got = _mask_applied_by_forward(B, H, N, 128, p, seed, dtype)
     want = oracle_lib.dropout_mask(B, H, N, N, np.float32(p).item(), seed)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("N,causal", [(640, False), (1024, False), (1024, True), (900, True)])
+def test_forward_kernel_mask_over_many_kv_tiles(N, causal):
+    # five to eight KV tiles per query tile: the keep bits pass through the helper warp's ring of four
+    # tiles several times, with an odd tile count (a last chunk of one tile) and, under the causal mask,
+    # a different tile count for every query tile
+    B, H, p, seed = 1, 2, 0.2, 11
+    got = _mask_applied_by_forward(B, H, N, 128, p, seed, torch.bfloat16, causal=causal)
+    want = oracle_lib.dropout_mask(B, H, N, N, np.float32(p).item(), seed)
+    if causal:
+        vis = np.tril(np.ones((N, N), dtype=bool))[None, None]
+        assert np.array_equal(got[np.broadcast_to(vis, got.shape)], want[np.broadcast_to(vis, want.shape)])
+    else:
+        assert np.array_equal(got, want)
 
 
 def test_forward_with_dropout_matches_oracle():
