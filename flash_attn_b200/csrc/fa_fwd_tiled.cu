@@ -111,6 +111,14 @@ struct Cfg {
     static constexpr int kSmemKeep = kSmemBar + 8 * kNumBars + 16;
     static constexpr int kSmemBytes = kSmemKeep + NQ * kKeepRing * 2 * 4 + 1024;  // + alignment slack
     static constexpr int kKeepWarp0 = NQ * 4 + 2;  // the helper warp of query tile i is kKeepWarp0 + i
+    // ALiBi whose bias is linear in the key position (every visible key at or before the query) is added by
+    // the tensor core: one more K = 16 step per Q K^T over two extra 64-column boxes, [1 1 0 ...] for every
+    // query row and [hi lo 0 ...] of slope * column / scale for every key row of a tile (two 16-bit terms
+    // carry the bias to 2^-17 relative).  Two-tile CTAs only: a single-tile CTA shares its SM.
+    static constexpr bool kBiasBoxes = NQ == 2;
+    static constexpr int kSmemBiasQ = (kSmemKeep + NQ * kKeepRing * 2 * 4 + 1023) / 1024 * 1024;
+    static constexpr int kSmemBiasK = kSmemBiasQ + kTile * 128;
+    static constexpr int kSmemBytesBias = kSmemBiasK + kTile * 128 + 1024;  // dynamic shared memory of the ALiBi kernels
 };
 
 struct TileRange {
@@ -287,6 +295,17 @@ __device__ __forceinline__ void issue_pv_rest(uint32_t d_tmem, uint32_t a_tmem, 
     asm volatile(FA_PV_HEAD FA_PV_STEP "}"
                  ::"r"(d_tmem), "r"(a_tmem + kSplitSteps * 8), "r"(vb_lo + kSplitSteps * 128), "r"(desc_hi), "r"(idesc), "r"(1u)
                  : "memory");
+}
+
+// One more k-step of S = Q K^T over the bias boxes (accumulating).
+__device__ __forceinline__ void issue_qk_bias(uint32_t d_tmem, uint32_t qa_lo, uint32_t kb_lo, uint32_t desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p1;\n\t.reg .b64 da, db;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p1;\n\t}"
+        ::"r"(d_tmem), "r"(qa_lo), "r"(kb_lo), "r"(desc_hi), "r"(idesc)
+        : "memory");
 }
 
 template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
@@ -471,6 +490,38 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
     }
     grid_dep_wait();  // every thread, before its first global access (the producer lane has passed it already)
+    // every unmasked key lies at or before the query: |q - k| = q - k, the ALiBi bias is linear in the key
+    const bool keys_not_after = a.is_causal || a.window_right == 0;
+    constexpr bool kBias = kAlibi && C::kBiasBoxes;
+    float bias_step = 0.0f;  // the bias of a column in units of the raw scores, per column
+    if constexpr (kBias) bias_step = a.alibi_slopes[unit % a.heads] * kLog2e / a.scale_log2;
+    // (fp16 operands: the largest entry, 127 columns, must stay far inside the format's range)
+    const bool bias_in_mma = kBias && keys_not_after && (kBf16 || fabsf(bias_step) < 200.0f);
+    if constexpr (kBias) {
+        if (bias_in_mma && n_union > 0 && threadIdx.x < kTile) {
+            const int rr = threadIdx.x;  // key row of the K box, query row of the Q box
+            const float x = bias_step * static_cast<float>(rr);
+            float hi_f, lo_f;
+            if constexpr (kBf16) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(x);
+                hi_f = __bfloat162float(h);
+                lo_f = x - hi_f;
+            } else {
+                const __half h = __float2half_rn(x);
+                hi_f = __half2float(h);
+                lo_f = x - hi_f;
+            }
+            const uint32_t kw = pack2<kBf16>(hi_f, lo_f), qw = pack2<kBf16>(1.0f, 1.0f);
+            const uint32_t krow = smem_base + C::kSmemBiasK + rr * 128, qrow = smem_base + C::kSmemBiasQ + rr * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {  // 16-byte chunks of the 128-byte-swizzled row
+                const uint32_t off = static_cast<uint32_t>(j ^ (rr & 7)) * 16;
+                st_shared_v4(krow + off, j == 0 ? kw : 0u, 0u, 0u, 0u);
+                st_shared_v4(qrow + off, j == 0 ? qw : 0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async_smem();
+        }
+    }
     FA_TR(92);
     tc_fence_before_sync();
     __syncthreads();
@@ -525,6 +576,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             auto issue_qk = [&](int i, int st) {
                 issue_qk_block<D>(tmem_base + i * kTile, q_lo + ((i * C::kTileBytes) >> 4),
                                   k_lo + ((st * C::kTileBytes) >> 4), desc_hi, idesc_qk);
+                if constexpr (kBias) {
+                    if (bias_in_mma)
+                        issue_qk_bias(tmem_base + i * kTile, static_cast<uint32_t>(dqk) | ((smem_base + C::kSmemBiasQ) >> 4),
+                                      static_cast<uint32_t>(dqk) | ((smem_base + C::kSmemBiasK) >> 4), desc_hi, idesc_qk);
+                }
             };
             auto issue_pv_a = [&](int i, int st, uint32_t accumulate) {
                 issue_pv_first(tmem_base + C::kTmemO + i * D, tmem_base + i * kTile,
@@ -624,8 +680,6 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         float l_sum = 0.0f;
         float slope2 = 0.0f;
         if constexpr (kAlibi) slope2 = a.alibi_slopes[unit % a.heads] * kLog2e;
-        // every unmasked key lies at or before the query: |q - k| = q - k
-        const bool keys_not_after = a.is_causal || a.window_right == 0;
         const float scale2 = a.scale_log2;
         // Dropout keep bits of this row for the KV tile at hand: bit 8*(2*(g%2) + w) + 7 - g/2 <-> columns
         // 8g..8g+7 of parity w; read from the table the keep-bit helper warp of this query tile fills.
@@ -697,9 +751,15 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             // tile max in log2 units.  Without ALiBi the max is taken over the raw scores
             // (softmax_scale > 0) and the scale is folded into the exponent's FMA.
             float m_tile;
+            // scores still unscaled (the scale is folded into the exponent's FMA) / the part of the ALiBi
+            // bias that is constant along the row, when the tensor core has added the part linear in the column
+            const bool raw_scores = !kAlibi || bias_in_mma;
+            float row_bias = 0.0f;
             if constexpr (kAlibi) {
                 const float dist0 = static_cast<float>(qpos - kbase);
-                if (keys_not_after) {
+                if (bias_in_mma) {
+                    row_bias = -slope2 * dist0;
+                } else if (keys_not_after) {
                     // bias of column c = slope*(c - dist0), built up pair by pair (one packed add and
                     // one packed FMA per two columns); the running sum is re-based every 16 columns
                     const float base = -slope2 * dist0;
@@ -735,6 +795,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
                 if constexpr (!kAlibi) m_tile *= scale2;
+                else if (raw_scores) m_tile = fmaf(m_tile, scale2, row_bias);
             }
             FA_TR(4);
 
@@ -766,8 +827,9 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 
             // P = exp2(s*scale - m), row sum over the undropped P (src/flash_forward.h:198-213, 221-237)
             float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-            const float2 neg_m2 = make_float2(neg_m, neg_m);
-            const float2 scale22 = make_float2(scale2, scale2);
+            const float add_m = kAlibi ? neg_m + row_bias : neg_m;
+            const float2 neg_m2 = make_float2(add_m, add_m);
+            const float2 scale22 = (!kAlibi || raw_scores) ? make_float2(scale2, scale2) : make_float2(1.0f, 1.0f);
             // Pairs kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.  The
             // polynomial needs finite arguments: on tiles with masked (-inf) scores its results for those
             // elements are replaced by 0 (MUFU gives 0 by itself).
@@ -789,8 +851,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                         for (int q = 0; q < 4; ++q) {
                             const int col = c * 32 + g * 8 + q * 2;
                             float2 x = make_float2(s[col], s[col + 1]);
-                            if constexpr (kAlibi) x = __fadd2_rn(x, neg_m2);
-                            else x = __ffma2_rn(x, scale22, neg_m2);
+                            x = __ffma2_rn(x, scale22, neg_m2);
                             float2 p;
                             if (q >= kPolyFrom) {
                                 p = poly_exp2_pair(x);
@@ -1020,7 +1081,8 @@ template <int D, int NQ, bool kBf16, bool kAlibi, bool kDropout>
 cudaError_t launch_one(FwdArgs a, const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv,
                        const CUtensorMap& to, int units, cudaStream_t stream) {
     auto kern = fwd_tiled_kernel<D, NQ, kBf16, kAlibi, kDropout>;
-    constexpr int smem = Cfg<D, NQ>::kSmemBytes;
+    constexpr int smem = (kAlibi && Cfg<D, NQ>::kBiasBoxes) ? Cfg<D, NQ>::kSmemBytesBias : Cfg<D, NQ>::kSmemBytes;
+    static_assert(smem <= 232448, "beyond the 227 KB a CTA may have");
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
