@@ -77,6 +77,21 @@ def test_alibi():
                                             window=(100, 0)), "alibi + causal + window")
 
 
+def test_alibi_far_keys_and_ring_positions():
+    # pure causal ALiBi over 1536 keys (the bias of the far tiles is large; the part linear in the key
+    # column comes from the tensor core, the row constant from the softmax), in both 16-bit formats, with a
+    # small softmax scale (large bias entries in units of the raw scores), and on a key block that lies
+    # wholly before the query block (positions as in a sequence ring: q_pos0 > k_pos0, no causal test)
+    gpu_util.assert_close(gpu_util.run_case(1, 4, 1536, 1536, 128, "bfloat16", seed=13, alibi=True, causal=True),
+                          "alibi causal bf16")
+    gpu_util.assert_close(gpu_util.run_case(1, 4, 1536, 1536, 128, "float16", seed=14, alibi=True, causal=True),
+                          "alibi causal fp16")
+    gpu_util.assert_close(gpu_util.run_case(1, 2, 512, 512, 64, "float16", seed=15, alibi=True, causal=True,
+                                            scale=0.01), "alibi causal fp16, small scale")
+    gpu_util.assert_close(gpu_util.run_case(1, 4, 512, 512, 128, "bfloat16", seed=16, alibi=True,
+                                            window=(-1, 0), q_pos0=2048, k_pos0=1024), "alibi, keys before queries")
+
+
 def test_config3_shape_scaled_down():
     # causal + window(1024, 0) + ALiBi slopes 2^(-8(h+1)/H), as config 3, at N = 2304
     gpu_util.assert_close(gpu_util.run_case(1, 4, 2304, 2304, 128, "bfloat16", seed=12, causal=True,
