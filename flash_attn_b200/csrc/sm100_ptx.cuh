@@ -89,7 +89,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
-// 3-D tiled load (no multicast): coordinates are (x = innermost element, y = row, z = batch*head).
+// 3-D tiled load into this CTA's own shared memory: coordinates are (x = innermost element, y = row, z = batch*head).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int x, int y, int z) {
     asm volatile(
