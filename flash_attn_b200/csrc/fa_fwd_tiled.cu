@@ -283,16 +283,16 @@ __device__ __forceinline__ void issue_qk_block(uint32_t d_tmem, uint32_t qa_lo, 
     "tcgen05.mma.cta_group::1.kind::f16 [%0], [pa], db, %4, p0;\n\t"
 // k-steps [0, kSplitSteps) of a tile: issued as soon as the first kSplitSteps*16 columns of P
 // are in tensor memory; the rest follow when P is complete.
-constexpr int kSplitSteps = 6;
+constexpr int kSplitSteps = 4;
 __device__ __forceinline__ void issue_pv_first(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
                                                uint32_t idesc, uint32_t accumulate) {
-    asm volatile(FA_PV_HEAD FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
+    asm volatile(FA_PV_HEAD FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
                  ::"r"(d_tmem), "r"(a_tmem), "r"(vb_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
                  : "memory");
 }
 __device__ __forceinline__ void issue_pv_rest(uint32_t d_tmem, uint32_t a_tmem, uint32_t vb_lo, uint32_t desc_hi,
                                               uint32_t idesc) {
-    asm volatile(FA_PV_HEAD FA_PV_STEP "}"
+    asm volatile(FA_PV_HEAD FA_PV_STEP FA_PV_STEP FA_PV_STEP "}"
                  ::"r"(d_tmem), "r"(a_tmem + kSplitSteps * 8), "r"(vb_lo + kSplitSteps * 128), "r"(desc_hi), "r"(idesc), "r"(1u)
                  : "memory");
 }
@@ -624,7 +624,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
 #pragma unroll
                     for (int i = 0; i < NQ; ++i) {
                         if (active(i, tile)) {
-                            // P V starts on the first three quarters of P while the last is exponentiated
+                            // P V starts on the first half of P while the second half is exponentiated
                             named_sync(1 + 2 * i);
                             FA_TR(21 + 10 * i);
                             tc_fence_after_sync();
