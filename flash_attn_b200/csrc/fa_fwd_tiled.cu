@@ -74,7 +74,12 @@ namespace fa {
 namespace {
 
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: rescale O only when the max grew by > 2^8
-constexpr int kPolyPairsFrom = 3;  // of every 4 column pairs, pairs >= this use the polynomial exp2
+// Which column pairs take the polynomial exp2: one pair of every four (a quarter of the elements), bit
+// 4*(g%2) + q = pair q of an even / odd group of eight columns.  The position decides how the cubic's FMAs
+// interleave with the MUFU results around them; measured over all sixteen placements, pair 0 everywhere is
+// the fastest without dropout and pairs 0 / 1 of even / odd groups with it (up to 2 % between placements).
+constexpr uint32_t kPolyMaskPlain = 0x11u;
+constexpr uint32_t kPolyMaskDropout = 0x21u;
 constexpr int kKeepChunk = 2;              // KV tiles whose dropout keep bits are handed over at a time (one Philox pass)
 constexpr int kKeepRing = 2 * kKeepChunk;  // tiles the keep-bit table holds
 constexpr float kLog2e = 1.4426950408889634f;
@@ -830,11 +835,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             const float add_m = kAlibi ? neg_m + row_bias : neg_m;
             const float2 neg_m2 = make_float2(add_m, add_m);
             const float2 scale22 = (!kAlibi || raw_scores) ? make_float2(scale2, scale2) : make_float2(1.0f, 1.0f);
-            // Pairs kPolyFrom..3 of every four go through poly_exp2_pair, the rest through MUFU ex2.  The
+            // The pairs of kPolyMask go through poly_exp2_pair, the rest through MUFU ex2.  The
             // polynomial needs finite arguments: on tiles with masked (-inf) scores its results for those
             // elements are replaced by 0 (MUFU gives 0 by itself).
-            auto exp_tile = [&](auto poly_tag, auto guard_tag) {
-                constexpr int kPolyFrom = decltype(poly_tag)::value;
+            auto exp_tile = [&](auto guard_tag) {
+                constexpr uint32_t kPolyMask = kDropout ? kPolyMaskDropout : kPolyMaskPlain;
                 constexpr bool kGuard = decltype(guard_tag)::value;  // the tile has masked (-inf) scores
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {  // quarters of 32 columns
@@ -853,7 +858,7 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                             float2 x = make_float2(s[col], s[col + 1]);
                             x = __ffma2_rn(x, scale22, neg_m2);
                             float2 p;
-                            if (q >= kPolyFrom) {
+                            if ((kPolyMask >> ((g & 1) * 4 + q)) & 1u) {
                                 p = poly_exp2_pair(x);
                                 if constexpr (kGuard) {
                                     // the polynomial gives 2^-126, not 0, for a masked score
@@ -879,8 +884,8 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
             };
-            if (tile_masked) exp_tile(std::integral_constant<int, kPolyPairsFrom>{}, std::true_type{});
-            else exp_tile(std::integral_constant<int, kPolyPairsFrom>{}, std::false_type{});
+            if (tile_masked) exp_tile(std::true_type{});
+            else exp_tile(std::false_type{});
             FA_TR(6);
             l_sum += (acc[0].x + acc[0].y) + (acc[1].x + acc[1].y) + (acc[2].x + acc[2].y) + (acc[3].x + acc[3].y);
             tmem_wait_st();
