@@ -500,8 +500,11 @@ fwd_tiled_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     constexpr bool kBias = kAlibi && C::kBiasBoxes;
     float bias_step = 0.0f;  // the bias of a column in units of the raw scores, per column
     if constexpr (kBias) bias_step = a.alibi_slopes[unit % a.heads] * kLog2e / a.scale_log2;
-    // (fp16 operands: the largest entry, 127 columns, must stay far inside the format's range)
-    const bool bias_in_mma = kBias && keys_not_after && (kBf16 || fabsf(bias_step) < 200.0f);
+    // (the two 16-bit terms carry an entry to 2^-17 relative: with slopes up to 4 per column in log2 units
+    // the bias is exact to 0.004, far below the 16-bit rounding of P; steeper slopes keep the softmax path.
+    // fp16 operands: the largest entry, 127 columns, must also stay far inside the format's range)
+    const bool bias_in_mma = kBias && keys_not_after && fabsf(bias_step * a.scale_log2) < 4.0f &&
+                             (kBf16 || fabsf(bias_step) < 200.0f);
     if constexpr (kBias) {
         if (bias_in_mma && n_union > 0 && threadIdx.x < kTile) {
             const int rr = threadIdx.x;  // key row of the K box, query row of the Q box

@@ -92,6 +92,22 @@ def test_alibi_far_keys_and_ring_positions():
                                             window=(-1, 0), q_pos0=2048, k_pos0=1024), "alibi, keys before queries")
 
 
+def test_alibi_steep_and_negative_slopes():
+    # slopes far outside the usual 2^(-8(h+1)/H): steep ones keep the bias in the softmax, negative ones
+    # (the sign the reference's own main() passes) go through the tensor core like any other
+    import flash_attn_b200 as fa
+    B, H, N, d = 1, 4, 512, 128
+    q, k, v = synth.qkv(17, B, H, N, N, d, "bfloat16", 1.0)
+    slopes = np.array([6.0, -0.5, 0.02, -3.0], dtype=np.float32)
+    scale = 1.0 / np.sqrt(d)
+    o, lse = fa.flash_attn_forward(gpu_util.to_dev(q, "bfloat16"), gpu_util.to_dev(k, "bfloat16"),
+                                   gpu_util.to_dev(v, "bfloat16"), softmax_scale=scale, causal=True,
+                                   alibi_slopes=torch.from_numpy(slopes))
+    want_o, want_lse = oracle_lib.forward(q, k, v, scale, causal=True, alibi_slopes=slopes)
+    assert np.abs(o.float().cpu().numpy() - want_o).max() < 2e-2
+    assert np.abs(lse.cpu().numpy() - want_lse).max() < 2e-3
+
+
 def test_config3_shape_scaled_down():
     # causal + window(1024, 0) + ALiBi slopes 2^(-8(h+1)/H), as config 3, at N = 2304
     gpu_util.assert_close(gpu_util.run_case(1, 4, 2304, 2304, 128, "bfloat16", seed=12, causal=True,
